@@ -94,8 +94,37 @@ SIGNATURES = {
     ),
 }
 
+# libb200_mixers.so (include/b200_mixers.h): ragged-batch mixers and feed-forward pieces
+MIXER_LIB_PATH = os.path.join(_PKG_DIR, "libb200_mixers.so")
+MIXER_SIGNATURES = {
+    "b200_mixers_abi_version": (c_int, []),
+    "b200_mixers_last_error": (c_char_p, []),
+    "b200_offset_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p]),
+    "b200_postnorm_residual": (
+        c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_float, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
+                c_void_p]),
+    "b200_value_prep_append": (
+        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_void_p,
+                c_int, c_int, c_int, c_int, c_int, c_int64, c_int, c_void_p]),
+    "b200_biased_attn_tile_tokens": (c_int, [c_int, c_int, c_int]),
+    "b200_biased_paged_attn": (
+        c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                c_void_p]),
+    "b200_gated_scan": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                c_int, c_int, c_int, c_void_p]),
+    "b200_head_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int, c_int, c_void_p]),
+    "b200_polynorm": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_float, c_int, c_int, c_int, c_void_p]),
+    "b200_sigmoid_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_scaled_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_clamped_glu": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_float, c_float, c_int, c_void_p]),
+    "b200_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+}
+
 _lock = threading.Lock()
 _lib = None
+_mixers = None
 
 
 class B200LibraryError(RuntimeError):
@@ -132,4 +161,50 @@ def load() -> ctypes.CDLL:
 def check(rc: int, what: str) -> None:
     if rc != 0:
         msg = load().b200_last_error()
+        raise B200LibraryError(f"{what} failed (code {rc}): {msg.decode() if msg else ''}")
+
+
+def _build_mixers() -> None:
+    """Compile libb200_mixers.so in-tree (one nvcc call, under a minute).  A checkout without built files compiles it
+    at first use; concurrent callers are serialised by a lock file and the library appears atomically."""
+    import fcntl
+    import subprocess
+
+    csrc = os.path.join(_PKG_DIR, "csrc")
+    with open(os.path.join(csrc, ".mixers.lock"), "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if os.path.exists(MIXER_LIB_PATH):
+            return
+        proc = subprocess.run(["make", "-C", csrc, "mixers"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        if proc.returncode != 0 or not os.path.exists(MIXER_LIB_PATH):
+            raise B200LibraryError("building libb200_mixers.so failed:\n" + proc.stdout.decode(errors="replace")[-4000:])
+
+
+def load_mixers() -> ctypes.CDLL:
+    """Load (once) libb200_mixers.so, building it first when the checkout has no built copy.  No CPU fallback."""
+    global _mixers
+    if _mixers is not None:
+        return _mixers
+    with _lock:
+        if _mixers is not None:
+            return _mixers
+        if not os.path.exists(MIXER_LIB_PATH):
+            _build_mixers()
+        try:
+            lib = ctypes.CDLL(MIXER_LIB_PATH)
+        except OSError as exc:
+            raise B200LibraryError(f"cannot load {MIXER_LIB_PATH}: {exc}") from exc
+        for name, (restype, argtypes) in MIXER_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = restype
+            fn.argtypes = argtypes
+        if lib.b200_mixers_abi_version() != 1:
+            raise B200LibraryError(f"mixers ABI version {lib.b200_mixers_abi_version()} != 1")
+        _mixers = lib
+    return _mixers
+
+
+def check_mixers(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load_mixers().b200_mixers_last_error()
         raise B200LibraryError(f"{what} failed (code {rc}): {msg.decode() if msg else ''}")

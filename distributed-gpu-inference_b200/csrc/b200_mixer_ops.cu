@@ -1,0 +1,712 @@
+// Sequence mixers and feed-forward pieces for decoder designs that keep an fp32 residual stream and run ragged
+// batches (prompt portions beside single decoded tokens, packed token-major):
+//
+//   offset RMS norm            y = x * rsqrt(mean(x^2) + eps) * (1 + w)            fp32 in, storage dtype out
+//   post-norm residual update  x += m * norm(y; w_post), optionally followed by the next sublayer's input norm
+//   value prep + paged append  per-head unit-RMS values, optional mix with an earlier layer's values, K/V scatter
+//                              into pools whose K and V rows have different widths
+//   biased paged attention     causal softmax attention of packed query rows over the paged cache with a learned
+//                              bias per (distance bucket, head), a per-position query temperature and a per-head
+//                              sigmoid output gate
+//   gated linear recurrence    S_t = diag(f_t) S_(t-1) + (1 - f_t) v_t^T, o_t = S_t^T q_t with the state in fp32,
+//                              carried per sequence in a slot pool; then a per-head weighted RMS norm
+//   PolyNorm activation        a N(z) + b N(z^2) + c N(z^3) + e over a token's feed-forward row
+//   sigmoid top-k routing, input-scaled expert rows, clamped GLU, combine
+//
+// Every constant of a design (eps, multipliers, temperatures, limits, table sizes) is a parameter.  Scores, softmax,
+// norms, gates of the recurrence, the state and the residual are fp32 whatever the storage dtype T is.  Summation
+// orders depend only on a token's own position and sizes, never on how a batch was cut, so a position's result does
+// not change with its neighbours in the batch.
+#include <algorithm>
+#include <type_traits>
+
+#include "../../include/b200_mixers.h"
+#include "b200_common.cuh"
+
+namespace b200 {
+
+// this file is a shared library of its own: it carries its own error buffer
+char* last_error_buf() {
+  static thread_local char buf[kErrBufLen] = {0};
+  return buf;
+}
+
+namespace {
+
+template <typename F>
+int mixer_by_dtype(int dtype, const char* name, F&& f) {
+  switch (dtype) {
+    case B200_DTYPE_F16:
+      return f(static_cast<__half*>(nullptr));
+    case B200_DTYPE_BF16:
+      return f(static_cast<__nv_bfloat16*>(nullptr));
+    case B200_DTYPE_F32:
+      return f(static_cast<float*>(nullptr));
+    default:
+      return fail(B200_EINVAL, "%s: unsupported dtype %d", name, dtype);
+  }
+}
+
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  // every thread returns the total; `red` holds 32 floats and may be reused after the call's second barrier
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ---- offset RMS norm ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+offset_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x, const T* __restrict__ w, float eps, int width) {
+  __shared__ float red[32];
+  const float* xr = x + static_cast<int64_t>(blockIdx.x) * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+  const float inv = rsqrtf(block_sum_256(ss, red) / static_cast<float>(width) + eps);
+  T* orow = out + static_cast<int64_t>(blockIdx.x) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    orow[i] = Cvt<T>::from_f32(xr[i] * inv * (1.0f + Cvt<T>::to_f32(w[i])));
+}
+
+// ---- x += mult * norm(y; w_post); optionally out_next = norm(x; w_next) ------------------------------------------
+// One CTA per token.  The updated row is kept in shared memory between the update and the second norm.
+template <typename T, typename Y>
+__global__ void __launch_bounds__(256)
+postnorm_residual_kernel(float* __restrict__ x, const Y* __restrict__ y, int64_t y_stride, const T* __restrict__ w_post,
+                         float mult, const T* __restrict__ w_next, T* __restrict__ out_next, float eps, int width) {
+  extern __shared__ float row_s[];
+  __shared__ float red[32];
+  const Y* yr = y + static_cast<int64_t>(blockIdx.x) * y_stride;
+  float* xr = x + static_cast<int64_t>(blockIdx.x) * width;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = Cvt<Y>::to_f32(yr[i]);
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = rsqrtf(block_sum_256(ss, red) / static_cast<float>(width) + eps);
+  float sx = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float n = Cvt<Y>::to_f32(yr[i]) * inv * (1.0f + Cvt<T>::to_f32(w_post[i]));
+    const float v = xr[i] + mult * n;
+    xr[i] = v;
+    row_s[i] = v;
+    sx = fmaf(v, v, sx);
+  }
+  if (w_next == nullptr) return;
+  const float inv2 = rsqrtf(block_sum_256(sx, red) / static_cast<float>(width) + eps);
+  T* orow = out_next + static_cast<int64_t>(blockIdx.x) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    orow[i] = Cvt<T>::from_f32(row_s[i] * inv2 * (1.0f + Cvt<T>::to_f32(w_next[i])));
+}
+
+// ---- value prep + K/V append ------------------------------------------------------------------------------------
+// One CTA per token, one warp per kv head (looping).  v <- v / rms(v) per head; with `v_prev` the stored value is
+// (1 - lam) v + lam v_prev.  The stored value also goes to `v_keep` (for later layers of the same step) when given.
+template <typename T>
+__global__ void __launch_bounds__(128)
+value_prep_append_kernel(const T* __restrict__ k, int64_t k_stride, const T* __restrict__ v, int64_t v_stride,
+                         const T* __restrict__ v_prev, T* __restrict__ v_keep, float lam, float eps,
+                         T* __restrict__ k_pool, T* __restrict__ v_pool, const int64_t* __restrict__ slot_mapping,
+                         int G, int dk, int dv, int block_size, int64_t max_blocks) {
+  const int tok = blockIdx.x;
+  const int64_t slot = slot_mapping[tok];
+  const int64_t blk = slot >= 0 ? slot / block_size : -1;
+  const bool store = blk >= 0 && blk < max_blocks;
+  const int off = store ? static_cast<int>(slot - blk * block_size) : 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int g = warp; g < G; g += nw) {
+    const T* vr = v + tok * v_stride + g * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) {
+      const float f = Cvt<T>::to_f32(vr[c]);
+      ss = fmaf(f, f, ss);
+    }
+    const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(dv) + eps);
+    T* dst = store ? v_pool + ((blk * G + g) * block_size + off) * dv : nullptr;
+    for (int c = lane; c < dv; c += 32) {
+      float f = Cvt<T>::to_f32(vr[c]) * inv;
+      if (v_prev) f = (1.0f - lam) * f + lam * Cvt<T>::to_f32(v_prev[static_cast<int64_t>(tok) * G * dv + g * dv + c]);
+      const T r = Cvt<T>::from_f32(f);
+      if (dst) dst[c] = r;
+      if (v_keep) v_keep[static_cast<int64_t>(tok) * G * dv + g * dv + c] = r;
+    }
+  }
+  if (store) {
+    for (int i = threadIdx.x; i < G * dk; i += blockDim.x) {
+      const int g = i / dk, d = i - g * dk;
+      k_pool[((blk * G + g) * block_size + off) * dk + d] = k[tok * k_stride + i];
+    }
+  }
+}
+
+// ---- biased paged attention over packed query rows ----------------------------------------------------------------
+// A CTA serves up to QT consecutive tokens of ONE sequence and one kv head: QT * (H / G) query rows.  Keys are
+// walked in tiles of 32 from position 0 (tile borders are fixed in the sequence, so the online-softmax order of a
+// position does not depend on how the prompt was cut).  K and V tiles sit in shared memory as fp32; a warp owns RW
+// rows, lane j scores key j of the tile, then the lanes split the value columns.
+struct AttnTile {
+  int tok0;   // first packed row of the tile
+  int count;  // tokens in the tile (<= QT)
+  int seq;    // row of the block table
+};
+
+constexpr int kAttnWarps = 8;
+constexpr int kKeyTile = 32;
+
+template <typename T, int RW, int DVL>
+__global__ void __launch_bounds__(kAttnWarps * 32)
+biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stride, const T* __restrict__ gate,
+                         int64_t gate_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                         const int32_t* __restrict__ block_tables, int table_stride, const AttnTile* __restrict__ tiles,
+                         const int32_t* __restrict__ tok_pos, const float* __restrict__ bias_lut, int lut_len,
+                         float scale, float temp_coef, int temp_every, int H, int G, int dk, int dv, int block_size) {
+  extern __shared__ float smem[];
+  const int dkp = (dk + 3) & ~3;            // padded row length of K / q rows (multiple of 4 floats)
+  const int ks = dkp + 4;                   // K row stride: 16-byte aligned and conflict-free for 128-bit reads
+  const int rep = H / G;
+  const AttnTile tile = tiles[blockIdx.x];
+  const int g = blockIdx.y;
+  const int n_rows = tile.count * rep;
+  float* k_s = smem;                        // [32][ks]
+  float* v_s = k_s + kKeyTile * ks;         // [32][dv]
+  float* q_s = v_s + kKeyTile * dv;         // [rows][dkp]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // query rows -> shared memory (fp32, zero padded)
+  for (int i = threadIdx.x; i < kAttnWarps * RW * dkp; i += blockDim.x) {
+    const int r = i / dkp, d = i - r * dkp;
+    const int t = r / rep, hh = g * rep + (r - t * rep);
+    q_s[i] = (r < n_rows && d < dk) ? Cvt<T>::to_f32(q[(tile.tok0 + t) * q_stride + hh * dk + d]) : 0.f;
+  }
+  const int pos_last = tok_pos[tile.tok0 + tile.count - 1];
+  const int32_t* table = block_tables + static_cast<int64_t>(tile.seq) * table_stride;
+
+  // per-row state of this warp's rows
+  float m[RW], l[RW], acc[RW][DVL], qmul[RW];
+  int pos[RW], head[RW];
+  bool live[RW];
+#pragma unroll
+  for (int r = 0; r < RW; ++r) {
+    const int row = warp * RW + r;
+    live[r] = row < n_rows;
+    const int t = live[r] ? row / rep : 0;
+    head[r] = g * rep + (live[r] ? row - t * rep : 0);
+    pos[r] = live[r] ? tok_pos[tile.tok0 + t] : -1;
+    const float steps = static_cast<float>((pos[r] + 1) / max(temp_every, 1));
+    qmul[r] = scale * (1.0f + temp_coef * logf(steps + 1.0f));
+    m[r] = -INFINITY;
+    l[r] = 0.f;
+#pragma unroll
+    for (int c = 0; c < DVL; ++c) acc[r][c] = 0.f;
+  }
+
+  for (int j0 = 0; j0 <= pos_last; j0 += kKeyTile) {
+    __syncthreads();  // previous tile fully consumed (and q_s written, first time round)
+    const int n_keys = min(kKeyTile, pos_last + 1 - j0);
+    for (int i = threadIdx.x; i < kKeyTile * dkp; i += blockDim.x) {
+      const int j = i / dkp, d = i - j * dkp;
+      float f = 0.f;
+      if (j < n_keys && d < dk) {
+        const int key = j0 + j;
+        const int64_t blk = table[key / block_size];
+        f = Cvt<T>::to_f32(k_pool[((blk * G + g) * block_size + key % block_size) * dk + d]);
+      }
+      k_s[j * ks + d] = f;
+    }
+    for (int i = threadIdx.x; i < kKeyTile * dv; i += blockDim.x) {
+      const int j = i / dv, c = i - j * dv;
+      float f = 0.f;
+      if (j < n_keys) {
+        const int key = j0 + j;
+        const int64_t blk = table[key / block_size];
+        f = Cvt<T>::to_f32(v_pool[((blk * G + g) * block_size + key % block_size) * dv + c]);
+      }
+      v_s[i] = f;
+    }
+    __syncthreads();
+
+    // scores: lane = key of the tile
+    float s[RW];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) s[r] = 0.f;
+    const float4* kr = reinterpret_cast<const float4*>(k_s + lane * ks);
+    for (int d4 = 0; d4 < dkp / 4; ++d4) {
+      const float4 kv = kr[d4];
+#pragma unroll
+      for (int r = 0; r < RW; ++r) {
+        const float4 qv = reinterpret_cast<const float4*>(q_s + (warp * RW + r) * dkp)[d4];  // broadcast read
+        s[r] = fmaf(qv.x, kv.x, s[r]);
+        s[r] = fmaf(qv.y, kv.y, s[r]);
+        s[r] = fmaf(qv.z, kv.z, s[r]);
+        s[r] = fmaf(qv.w, kv.w, s[r]);
+      }
+    }
+    float p[RW];
+#pragma unroll
+    for (int r = 0; r < RW; ++r) {
+      const int key = j0 + lane;
+      const bool seen = live[r] && key <= pos[r];
+      const bool any = live[r] && j0 <= pos[r];  // warp-uniform
+      float sc = -INFINITY;
+      if (seen) {
+        const int dist = min(pos[r] - key, lut_len - 1);
+        sc = s[r] * qmul[r] + bias_lut[head[r] * lut_len + dist];
+      }
+      p[r] = 0.f;
+      if (any) {
+        const float m_new = fmaxf(m[r], warp_max(sc));
+        const float corr = expf(m[r] - m_new);
+        p[r] = seen ? expf(sc - m_new) : 0.f;
+        l[r] = l[r] * corr + warp_sum(p[r]);
+        m[r] = m_new;
+#pragma unroll
+        for (int c = 0; c < DVL; ++c) acc[r][c] *= corr;
+      }
+    }
+    // values: lane = column (plus 32 c)
+    for (int j = 0; j < n_keys; ++j) {
+      float vv[DVL];
+#pragma unroll
+      for (int c = 0; c < DVL; ++c) {
+        const int col = lane + 32 * c;
+        vv[c] = col < dv ? v_s[j * dv + col] : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < RW; ++r) {
+        const float pj = __shfl_sync(0xffffffffu, p[r], j);
+#pragma unroll
+        for (int c = 0; c < DVL; ++c) acc[r][c] = fmaf(pj, vv[c], acc[r][c]);
+      }
+    }
+  }
+
+#pragma unroll
+  for (int r = 0; r < RW; ++r) {
+    if (!live[r]) continue;
+    const int row = warp * RW + r;
+    const int t = row / rep;
+    const int64_t n = tile.tok0 + t;
+    const float gt = gate ? sigmoidf_(Cvt<T>::to_f32(gate[n * gate_stride + head[r]])) : 1.0f;
+    const float inv = gt / l[r];
+#pragma unroll
+    for (int c = 0; c < DVL; ++c) {
+      const int col = lane + 32 * c;
+      if (col < dv) out[(n * H + head[r]) * dv + col] = Cvt<T>::from_f32(acc[r][c] * inv);
+    }
+  }
+}
+
+// ---- gated linear recurrence ------------------------------------------------------------------------------------
+// One CTA per (sequence, head).  The state [dk][dv] lives in shared memory for the whole portion; thread (rg, c)
+// owns column c and the rows i = rg, rg + RG, ...  Inputs of token t + 1 are fetched while token t is computed.
+struct ScanSeq {
+  int tok0;   // first packed row
+  int count;  // tokens of this sequence in the step
+  int slot;   // state slot
+  int fresh;  // 1: the sequence starts here, the state is zero
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_scan_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, const T* __restrict__ zf, const T* __restrict__ v,
+                  int64_t in_stride, const T* __restrict__ f_bias, const T* __restrict__ lower, float* __restrict__ state,
+                  const ScanSeq* __restrict__ seqs, int H, int dk, int dv, int TC) {
+  extern __shared__ float smem[];
+  const ScanSeq sq = seqs[blockIdx.x];
+  const int h = blockIdx.y;
+  const int RG = blockDim.x / TC;
+  const int c0 = threadIdx.x % TC, rg = threadIdx.x / TC;
+  float* S = smem;                         // [dk][dv]
+  float* in_s = S + dk * dv;               // 2 x (q[dk], f[dk], v[dv])
+  const int in_len = 2 * dk + dv;
+  float* part = in_s + 2 * in_len;         // [RG][dv]
+  float* st = state + (static_cast<int64_t>(sq.slot) * H + h) * dk * dv;
+  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) S[i] = sq.fresh ? 0.f : st[i];
+
+  auto fetch = [&](int t, float* dst) {
+    const int64_t row = static_cast<int64_t>(sq.tok0 + t) * in_stride;
+    for (int i = threadIdx.x; i < in_len; i += blockDim.x) {
+      float r;
+      if (i < dk) {
+        const float z = Cvt<T>::to_f32(zq[row + h * dk + i]);
+        r = z * sigmoidf_(z);
+      } else if (i < 2 * dk) {
+        const int d = h * dk + (i - dk);
+        const float lo = Cvt<T>::to_f32(lower[d]);
+        r = lo + (1.0f - lo) * sigmoidf_(Cvt<T>::to_f32(zf[row + d]) + Cvt<T>::to_f32(f_bias[d]));
+      } else {
+        r = Cvt<T>::to_f32(v[row + h * dv + (i - 2 * dk)]);
+      }
+      dst[i] = r;
+    }
+  };
+  fetch(0, in_s);
+  __syncthreads();
+  for (int t = 0; t < sq.count; ++t) {
+    const float* cur = in_s + (t & 1) * in_len;
+    if (t + 1 < sq.count) fetch(t + 1, in_s + ((t + 1) & 1) * in_len);
+    for (int c = c0; c < dv; c += TC) {
+      const float vc = cur[2 * dk + c];
+      float sum = 0.f;
+      for (int i = rg; i < dk; i += RG) {
+        const float f = cur[dk + i];
+        const float s_new = f * S[i * dv + c] + (1.0f - f) * vc;
+        S[i * dv + c] = s_new;
+        sum = fmaf(s_new, cur[i], sum);
+      }
+      part[rg * dv + c] = sum;
+    }
+    __syncthreads();
+    if (rg == 0) {
+      for (int c = c0; c < dv; c += TC) {
+        float o = 0.f;
+        for (int r = 0; r < RG; ++r) o += part[r * dv + c];
+        o_raw[(static_cast<int64_t>(sq.tok0 + t) * H + h) * dv + c] = o;
+      }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) st[i] = S[i];
+}
+
+// per-head weighted RMS norm of fp32 rows [rows, dv] -> T; one warp per row
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_rmsnorm_kernel(T* __restrict__ out, const float* __restrict__ x, const T* __restrict__ w, float eps, int64_t rows,
+                    int dv) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float* xr = x + row * dv;
+  float ss = 0.f;
+  for (int c = lane; c < dv; c += 32) ss = fmaf(xr[c], xr[c], ss);
+  const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(dv) + eps);
+  for (int c = lane; c < dv; c += 32) out[row * dv + c] = Cvt<T>::from_f32(xr[c] * inv * Cvt<T>::to_f32(w[c]));
+}
+
+// ---- PolyNorm ---------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+polynorm_kernel(T* __restrict__ out, const T* __restrict__ z, int64_t z_stride, const T* __restrict__ coef, float eps,
+                int ff) {
+  __shared__ float red[32];
+  const T* zr = z + static_cast<int64_t>(blockIdx.x) * z_stride;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int i = threadIdx.x; i < ff; i += blockDim.x) {
+    const float a = Cvt<T>::to_f32(zr[i]);
+    const float a2 = a * a, a3 = a2 * a;
+    s1 = fmaf(a, a, s1);
+    s2 = fmaf(a2, a2, s2);
+    s3 = fmaf(a3, a3, s3);
+  }
+  const float n = static_cast<float>(ff);
+  const float i1 = rsqrtf(block_sum_256(s1, red) / n + eps);
+  const float i2 = rsqrtf(block_sum_256(s2, red) / n + eps);
+  const float i3 = rsqrtf(block_sum_256(s3, red) / n + eps);
+  const float ca = Cvt<T>::to_f32(coef[0]), cb = Cvt<T>::to_f32(coef[1]), cc = Cvt<T>::to_f32(coef[2]),
+              ce = Cvt<T>::to_f32(coef[3]);
+  T* orow = out + static_cast<int64_t>(blockIdx.x) * ff;
+  for (int i = threadIdx.x; i < ff; i += blockDim.x) {
+    const float a = Cvt<T>::to_f32(zr[i]);
+    const float a2 = a * a;
+    orow[i] = Cvt<T>::from_f32(ca * a * i1 + cb * a2 * i2 + cc * a2 * a * i3 + ce);
+  }
+}
+
+// ---- routing ----------------------------------------------------------------------------------------------------
+// One warp per token: the `top` largest logits (ties: lowest index), weight = sigmoid(logit).
+__global__ void __launch_bounds__(128)
+sigmoid_topk_kernel(int32_t* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits, int n_tok,
+                    int E, int top) {
+  const int tok = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (tok >= n_tok) return;
+  const int lane = threadIdx.x & 31;
+  const float* z = logits + static_cast<int64_t>(tok) * E;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      bool taken = false;
+      for (int j = 0; j < k; ++j) taken |= ids[static_cast<int64_t>(tok) * top + j] == e;
+      const float f = z[e];
+      if (!taken && (f > best || (f == best && e < bi))) {
+        best = f;
+        bi = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) {
+        best = ob;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      ids[static_cast<int64_t>(tok) * top + k] = bi;
+      weights[static_cast<int64_t>(tok) * top + k] = sigmoidf_(best);
+    }
+    __syncwarp();
+  }
+}
+
+// rows of the expert-sorted input: xs[r] = T(w[src[r]] * h[src[r] / top])
+template <typename T>
+__global__ void __launch_bounds__(256)
+scaled_gather_kernel(T* __restrict__ xs, const T* __restrict__ h, const float* __restrict__ weights,
+                     const int64_t* __restrict__ src, int top, int width) {
+  const int64_t pair = src[blockIdx.x];
+  const float w = weights[pair];
+  const T* hr = h + (pair / top) * width;
+  T* o = xs + static_cast<int64_t>(blockIdx.x) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = Cvt<T>::from_f32(w * Cvt<T>::to_f32(hr[i]));
+}
+
+// y = g' * sigmoid(alpha g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit); gu rows hold g | u
+template <typename T>
+__global__ void __launch_bounds__(256)
+clamped_glu_kernel(T* __restrict__ y, const T* __restrict__ gu, int64_t rows, int ff, float limit, float alpha) {
+  const int64_t n = rows * ff;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / ff;
+    const int c = static_cast<int>(i - r * ff);
+    const float g = fminf(Cvt<T>::to_f32(gu[r * 2 * ff + c]), limit);
+    const float u = fminf(fmaxf(Cvt<T>::to_f32(gu[r * 2 * ff + ff + c]), -limit), limit);
+    y[i] = Cvt<T>::from_f32(g * sigmoidf_(alpha * g) * (u + 1.0f));
+  }
+}
+
+// out[n] = sum_k ys[where[n * top + k]] in fp32, k ascending
+template <typename T>
+__global__ void __launch_bounds__(256)
+expert_combine_kernel(float* __restrict__ out, const T* __restrict__ ys, const int64_t* __restrict__ where, int top,
+                      int width) {
+  const int64_t n = blockIdx.x;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) a += Cvt<T>::to_f32(ys[where[n * top + k] * width + i]);
+    out[n * width + i] = a;
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_mixers_abi_version(void) { return B200_MIXERS_ABI_VERSION; }
+
+const char* b200_mixers_last_error(void) { return last_error_buf(); }
+
+int b200_offset_rmsnorm(void* out, const float* x, const void* weight, float eps, int rows, int width, int dtype,
+                        void* stream) {
+  if (rows < 0 || width <= 0) return fail(B200_EINVAL, "b200_offset_rmsnorm: bad sizes");
+  if (rows == 0) return 0;
+  if (!out || !x || !weight) return fail(B200_EINVAL, "b200_offset_rmsnorm: null pointer");
+  return mixer_by_dtype(dtype, "b200_offset_rmsnorm", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    offset_rmsnorm_kernel<T><<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<T*>(out), x, static_cast<const T*>(weight), eps, width);
+    return check_launch("b200_offset_rmsnorm");
+  });
+}
+
+int b200_postnorm_residual(float* x, const void* y, int64_t y_stride, int y_is_f32, const void* w_post, float mult,
+                           const void* w_next, void* out_next, float eps, int rows, int width, int dtype, void* stream) {
+  if (rows < 0 || width <= 0 || width > 40000) return fail(B200_EINVAL, "b200_postnorm_residual: bad sizes");
+  if (rows == 0) return 0;
+  if (!x || !y || !w_post || (w_next && !out_next)) return fail(B200_EINVAL, "b200_postnorm_residual: null pointer");
+  const size_t smem = static_cast<size_t>(width) * sizeof(float);
+  return mixer_by_dtype(dtype, "b200_postnorm_residual", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    auto launch = [&](auto kern, auto* ytag) {
+      using Y = std::remove_pointer_t<decltype(ytag)>;
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      kern<<<rows, 256, smem, static_cast<cudaStream_t>(stream)>>>(x, static_cast<const Y*>(y), y_stride,
+                                                                  static_cast<const T*>(w_post), mult,
+                                                                  static_cast<const T*>(w_next), static_cast<T*>(out_next),
+                                                                  eps, width);
+    };
+    if (y_is_f32) launch(postnorm_residual_kernel<T, float>, static_cast<float*>(nullptr));
+    else launch(postnorm_residual_kernel<T, T>, static_cast<T*>(nullptr));
+    return check_launch("b200_postnorm_residual");
+  });
+}
+
+int b200_value_prep_append(const void* k, int64_t k_stride, const void* v, int64_t v_stride, const void* v_prev,
+                           void* v_keep, float lam, float eps, void* k_pool, void* v_pool, const int64_t* slot_mapping,
+                           int n_tok, int G, int dk, int dv, int block_size, int64_t max_blocks, int dtype, void* stream) {
+  if (n_tok < 0 || G <= 0 || dk <= 0 || dv <= 0 || block_size <= 0) return fail(B200_EINVAL, "b200_value_prep_append: bad sizes");
+  if (n_tok == 0) return 0;
+  if (!k || !v || !k_pool || !v_pool || !slot_mapping) return fail(B200_EINVAL, "b200_value_prep_append: null pointer");
+  return mixer_by_dtype(dtype, "b200_value_prep_append", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    value_prep_append_kernel<T><<<n_tok, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const T*>(k), k_stride, static_cast<const T*>(v), v_stride, static_cast<const T*>(v_prev),
+        static_cast<T*>(v_keep), lam, eps, static_cast<T*>(k_pool), static_cast<T*>(v_pool), slot_mapping, G, dk, dv,
+        block_size, max_blocks);
+    return check_launch("b200_value_prep_append");
+  });
+}
+
+int b200_biased_attn_tile_tokens(int n_tokens_in_portion, int H, int G) {
+  // tokens per CTA: prompt portions fill 8 warps x 4 rows, a decoded token takes what its head group needs
+  const int rep = std::max(1, H / std::max(G, 1));
+  const int rows_max = kAttnWarps * 4;
+  return std::max(1, std::min(n_tokens_in_portion, rows_max / std::min(rep, rows_max)));
+}
+
+int b200_biased_paged_attn(void* out, const void* q, int64_t q_stride, const void* gate, int64_t gate_stride,
+                           const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
+                           const int32_t* tiles, int n_tiles, int max_tile_tokens, const int32_t* tok_pos,
+                           const float* bias_lut, int lut_len, float scale, float temp_coef, int temp_every, int H, int G,
+                           int dk, int dv, int block_size, int dtype, void* stream) {
+  if (n_tiles < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || dv > 256 || block_size <= 0 || lut_len <= 0 ||
+      max_tile_tokens <= 0)
+    return fail(B200_EINVAL, "b200_biased_paged_attn: bad sizes");
+  if (n_tiles == 0) return 0;
+  if (!out || !q || !k_pool || !v_pool || !block_tables || !tiles || !tok_pos || !bias_lut)
+    return fail(B200_EINVAL, "b200_biased_paged_attn: null pointer");
+  const int rep = H / G;
+  const int rows = max_tile_tokens * rep;
+  if (rows > kAttnWarps * 4) return fail(B200_ESHAPE, "b200_biased_paged_attn: %d rows per tile > %d", rows, kAttnWarps * 4);
+  const int dkp = (dk + 3) & ~3;
+  const int rw = rows <= kAttnWarps ? 1 : (rows <= 2 * kAttnWarps ? 2 : 4);  // rows per warp (template RW)
+  const size_t smem = sizeof(float) * (static_cast<size_t>(kKeyTile) * (dkp + 4) + static_cast<size_t>(kKeyTile) * dv +
+                                       static_cast<size_t>(kAttnWarps) * rw * dkp);
+  if (smem > 200 * 1024) return fail(B200_ESHAPE, "b200_biased_paged_attn: head sizes %d / %d need too much shared memory", dk, dv);
+  const dim3 grid(n_tiles, G);
+  return mixer_by_dtype(dtype, "b200_biased_paged_attn", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    auto launch = [&](auto kern) {
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      kern<<<grid, kAttnWarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+          static_cast<T*>(out), static_cast<const T*>(q), q_stride, static_cast<const T*>(gate), gate_stride,
+          static_cast<const T*>(k_pool), static_cast<const T*>(v_pool), block_tables, table_stride,
+          reinterpret_cast<const AttnTile*>(tiles), tok_pos, bias_lut, lut_len, scale, temp_coef, temp_every, H, G, dk, dv,
+          block_size);
+    };
+    const int dvl = (dv + 31) / 32;
+#define B200_ATTN_CASE(RW_)                                                  \
+  if (dvl <= 1) launch(biased_paged_attn_kernel<T, RW_, 1>);                 \
+  else if (dvl <= 2) launch(biased_paged_attn_kernel<T, RW_, 2>);            \
+  else if (dvl <= 4) launch(biased_paged_attn_kernel<T, RW_, 4>);            \
+  else launch(biased_paged_attn_kernel<T, RW_, 8>);
+    if (rw <= 1) { B200_ATTN_CASE(1) }
+    else if (rw <= 2) { B200_ATTN_CASE(2) }
+    else { B200_ATTN_CASE(4) }
+#undef B200_ATTN_CASE
+    return check_launch("b200_biased_paged_attn");
+  });
+}
+
+int b200_gated_scan(float* o_raw, const void* zq, const void* zf, const void* v, int64_t in_stride, const void* f_bias,
+                    const void* lower, float* state, const int32_t* seqs, int n_seqs, int H, int dk, int dv, int dtype,
+                    void* stream) {
+  if (n_seqs < 0 || H <= 0 || dk <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_gated_scan: bad sizes");
+  if (n_seqs == 0) return 0;
+  if (!o_raw || !zq || !zf || !v || !f_bias || !lower || !state || !seqs) return fail(B200_EINVAL, "b200_gated_scan: null pointer");
+  int TC = 1;
+  while (TC < dv && TC < 256) TC <<= 1;
+  const int RG = 256 / TC;
+  const size_t smem = sizeof(float) * (static_cast<size_t>(dk) * dv + 2 * (2 * static_cast<size_t>(dk) + dv) +
+                                       static_cast<size_t>(RG) * dv);
+  if (smem > 200 * 1024) return fail(B200_ESHAPE, "b200_gated_scan: state %d x %d does not fit shared memory", dk, dv);
+  const dim3 grid(n_seqs, H);
+  return mixer_by_dtype(dtype, "b200_gated_scan", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    auto kern = gated_scan_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+        o_raw, static_cast<const T*>(zq), static_cast<const T*>(zf), static_cast<const T*>(v), in_stride,
+        static_cast<const T*>(f_bias), static_cast<const T*>(lower), state, reinterpret_cast<const ScanSeq*>(seqs), H, dk,
+        dv, TC);
+    return check_launch("b200_gated_scan");
+  });
+}
+
+int b200_head_rmsnorm(void* out, const float* x, const void* weight, float eps, int64_t rows, int dv, int dtype,
+                      void* stream) {
+  if (rows < 0 || dv <= 0) return fail(B200_EINVAL, "b200_head_rmsnorm: bad sizes");
+  if (rows == 0) return 0;
+  if (!out || !x || !weight) return fail(B200_EINVAL, "b200_head_rmsnorm: null pointer");
+  return mixer_by_dtype(dtype, "b200_head_rmsnorm", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    head_rmsnorm_kernel<T><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<T*>(out), x, static_cast<const T*>(weight), eps, rows, dv);
+    return check_launch("b200_head_rmsnorm");
+  });
+}
+
+int b200_polynorm(void* out, const void* z, int64_t z_stride, const void* coef, float eps, int rows, int ff, int dtype,
+                  void* stream) {
+  if (rows < 0 || ff <= 0) return fail(B200_EINVAL, "b200_polynorm: bad sizes");
+  if (rows == 0) return 0;
+  if (!out || !z || !coef) return fail(B200_EINVAL, "b200_polynorm: null pointer");
+  return mixer_by_dtype(dtype, "b200_polynorm", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    polynorm_kernel<T><<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<T*>(out), static_cast<const T*>(z), z_stride, static_cast<const T*>(coef), eps, ff);
+    return check_launch("b200_polynorm");
+  });
+}
+
+int b200_sigmoid_topk(int32_t* ids, float* weights, const float* logits, int n_tok, int E, int top, void* stream) {
+  if (n_tok < 0 || E <= 0 || top <= 0 || top > E) return fail(B200_EINVAL, "b200_sigmoid_topk: bad sizes");
+  if (n_tok == 0) return 0;
+  if (!ids || !weights || !logits) return fail(B200_EINVAL, "b200_sigmoid_topk: null pointer");
+  sigmoid_topk_kernel<<<(n_tok + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(ids, weights, logits, n_tok, E, top);
+  return check_launch("b200_sigmoid_topk");
+}
+
+int b200_scaled_gather(void* xs, const void* h, const float* weights, const int64_t* src, int64_t n_rows, int top,
+                       int width, int dtype, void* stream) {
+  if (n_rows < 0 || top <= 0 || width <= 0) return fail(B200_EINVAL, "b200_scaled_gather: bad sizes");
+  if (n_rows == 0) return 0;
+  if (!xs || !h || !weights || !src) return fail(B200_EINVAL, "b200_scaled_gather: null pointer");
+  return mixer_by_dtype(dtype, "b200_scaled_gather", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    scaled_gather_kernel<T><<<static_cast<unsigned>(n_rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<T*>(xs), static_cast<const T*>(h), weights, src, top, width);
+    return check_launch("b200_scaled_gather");
+  });
+}
+
+int b200_clamped_glu(void* y, const void* gu, int64_t rows, int ff, float limit, float alpha, int dtype, void* stream) {
+  if (rows < 0 || ff <= 0) return fail(B200_EINVAL, "b200_clamped_glu: bad sizes");
+  if (rows == 0) return 0;
+  if (!y || !gu) return fail(B200_EINVAL, "b200_clamped_glu: null pointer");
+  const int64_t n = rows * ff;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((n + 255) / 256, 148 * 16));
+  return mixer_by_dtype(dtype, "b200_clamped_glu", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    clamped_glu_kernel<T><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<T*>(y), static_cast<const T*>(gu),
+                                                                               rows, ff, limit, alpha);
+    return check_launch("b200_clamped_glu");
+  });
+}
+
+int b200_expert_combine(float* out, const void* ys, const int64_t* where, int64_t n_tok, int top, int width, int dtype,
+                        void* stream) {
+  if (n_tok < 0 || top <= 0 || width <= 0) return fail(B200_EINVAL, "b200_expert_combine: bad sizes");
+  if (n_tok == 0) return 0;
+  if (!out || !ys || !where) return fail(B200_EINVAL, "b200_expert_combine: null pointer");
+  return mixer_by_dtype(dtype, "b200_expert_combine", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    expert_combine_kernel<T><<<static_cast<unsigned>(n_tok), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        out, static_cast<const T*>(ys), where, top, width);
+    return check_launch("b200_expert_combine");
+  });
+}
+
+}  // extern "C"

@@ -1,0 +1,205 @@
+"""Torch-tensor front end of libb200_mixers.so (include/b200_mixers.h): ragged-batch mixers and feed-forward pieces.
+
+Same rules as ``ops``: shapes are checked on the host, raw device pointers and torch's current stream go to the
+library, nothing here computes and nothing falls back to torch.  Activations of a step are packed ``[n_tok, ...]``.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .ops import DTYPE_ID, _need_cuda, _stream
+
+
+def _lib_():
+    return _lib.load_mixers()
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _rows2(x: torch.Tensor) -> int:
+    """Row stride of a 2-D view whose last dimension is contiguous."""
+    if x.dim() != 2 or (x.shape[1] > 1 and x.stride(1) != 1):
+        raise ValueError("expected a 2-D tensor with a contiguous last dimension")
+    return x.stride(0) if x.shape[0] > 1 else max(x.stride(0), x.shape[1])
+
+
+def offset_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """``x * rsqrt(mean(x^2) + eps) * (1 + weight)``: fp32 ``[rows, width]`` in, the weight's dtype out."""
+    _need_cuda(x, weight)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2:
+        raise ValueError("the residual stream is a contiguous fp32 [rows, width] tensor")
+    out = torch.empty(x.shape, dtype=weight.dtype, device=x.device)
+    rc = _lib_().b200_offset_rmsnorm(out.data_ptr(), x.data_ptr(), weight.data_ptr(), float(eps), x.shape[0], x.shape[1],
+                                     DTYPE_ID[weight.dtype], _stream())
+    _lib.check_mixers(rc, "b200_offset_rmsnorm")
+    return out
+
+
+def postnorm_residual(x: torch.Tensor, y: torch.Tensor, w_post: torch.Tensor, mult: float, eps: float,
+                      w_next: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """In place ``x += mult * offset_norm(y; w_post)`` (fp32); returns ``offset_norm(x; w_next)`` in the weights'
+    dtype when ``w_next`` is given.  ``y``: the weights' dtype or fp32."""
+    _need_cuda(x, y, w_post)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2 or y.shape != x.shape:
+        raise ValueError("x must be contiguous fp32 [rows, width] and y of the same shape")
+    if y.dtype not in (w_post.dtype, torch.float32):
+        raise TypeError("y must have the weights' dtype or be fp32")
+    out = torch.empty(x.shape, dtype=w_post.dtype, device=x.device) if w_next is not None else None
+    rc = _lib_().b200_postnorm_residual(x.data_ptr(), y.data_ptr(), _rows2(y), int(y.dtype == torch.float32 and
+                                        w_post.dtype != torch.float32), w_post.data_ptr(), float(mult), _ptr(w_next),
+                                        _ptr(out), float(eps), x.shape[0], x.shape[1], DTYPE_ID[w_post.dtype], _stream())
+    _lib.check_mixers(rc, "b200_postnorm_residual")
+    return out
+
+
+def value_prep_append(k: torch.Tensor, v: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                      slot_mapping: torch.Tensor, eps: float, v_prev: Optional[torch.Tensor] = None, lam: float = 0.0,
+                      v_keep: Optional[torch.Tensor] = None) -> None:
+    """Unit-RMS values per head (optionally mixed with ``v_prev``), then k / v into the pools at ``slot_mapping``.
+    ``k [n, G*dk]``, ``v [n, G*dv]`` (column slices of a projection are fine); pools ``[blocks, G, bs, dk|dv]``."""
+    _need_cuda(k, v, k_pool, v_pool, slot_mapping)
+    nb, G, bs, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    n = k.shape[0]
+    if k.shape[1] != G * dk or v.shape != (n, G * dv) or tuple(v_pool.shape[:3]) != (nb, G, bs):
+        raise ValueError("k / v do not match the pools")
+    if slot_mapping.dtype != torch.int64 or slot_mapping.numel() != n:
+        raise ValueError("slot_mapping must be int64 [n_tok]")
+    for t in (v_prev, v_keep):
+        if t is not None and (tuple(t.shape) != (n, G * dv) or not t.is_contiguous() or t.dtype != v.dtype):
+            raise ValueError("v_prev / v_keep must be contiguous [n_tok, G*dv] in the storage dtype")
+    rc = _lib_().b200_value_prep_append(k.data_ptr(), _rows2(k), v.data_ptr(), _rows2(v), _ptr(v_prev), _ptr(v_keep),
+                                        float(lam), float(eps), k_pool.data_ptr(), v_pool.data_ptr(),
+                                        slot_mapping.data_ptr(), n, G, dk, dv, bs, nb, DTYPE_ID[k_pool.dtype], _stream())
+    _lib.check_mixers(rc, "b200_value_prep_append")
+
+
+def attn_tile_tokens(n_tokens: int, H: int, G: int) -> int:
+    return int(_lib_().b200_biased_attn_tile_tokens(int(n_tokens), H, G))
+
+
+def biased_paged_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: torch.Tensor,
+                           block_tables: torch.Tensor, tiles: torch.Tensor, max_tile_tokens: int, tok_pos: torch.Tensor,
+                           bias_lut: torch.Tensor, scale: float, temp_coef: float, temp_every: int, H: int) -> torch.Tensor:
+    """Causal attention of packed rows ``q [n, H*dk]`` over the paged cache with a distance-bias table
+    ``bias_lut [H, L]`` (fp32), a query temperature and a sigmoid gate ``gate [n, H]``; returns ``[n, H*dv]``."""
+    _need_cuda(q, k_pool, v_pool, block_tables, tiles, tok_pos, bias_lut)
+    nb, G, bs, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    n = q.shape[0]
+    if q.shape[1] != H * dk or (gate is not None and tuple(gate.shape) != (n, H)):
+        raise ValueError("q / gate do not match the head layout")
+    if block_tables.dtype != torch.int32 or tiles.dtype != torch.int32 or tok_pos.dtype != torch.int32:
+        raise TypeError("block tables, tiles and positions are int32")
+    if tiles.dim() != 2 or tiles.shape[1] != 3 or not tiles.is_contiguous():
+        raise ValueError("tiles must be contiguous int32 [n_tiles, 3]")
+    if bias_lut.dtype != torch.float32 or bias_lut.shape[0] != H or not bias_lut.is_contiguous():
+        raise ValueError("bias_lut must be contiguous fp32 [H, L]")
+    out = torch.empty((n, H * dv), dtype=q.dtype, device=q.device)
+    rc = _lib_().b200_biased_paged_attn(out.data_ptr(), q.data_ptr(), _rows2(q), _ptr(gate),
+                                        _rows2(gate) if gate is not None else 0, k_pool.data_ptr(), v_pool.data_ptr(),
+                                        block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(), tiles.shape[0],
+                                        int(max_tile_tokens), tok_pos.data_ptr(), bias_lut.data_ptr(), bias_lut.shape[1],
+                                        float(scale), float(temp_coef), int(temp_every), H, G, dk, dv, bs,
+                                        DTYPE_ID[q.dtype], _stream())
+    _lib.check_mixers(rc, "b200_biased_paged_attn")
+    return out
+
+
+def gated_scan(zq: torch.Tensor, zf: torch.Tensor, v: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor,
+               state: torch.Tensor, seqs: torch.Tensor, H: int) -> torch.Tensor:
+    """Gated linear recurrence over each sequence's tokens; ``state`` fp32 ``[slots, H, dk, dv]`` is read (unless the
+    sequence is fresh) and written back.  ``zq / zf [n, H*dk]``, ``v [n, H*dv]`` are column slices of ONE projection
+    (same row stride).  Returns the raw read-outs, fp32 ``[n, H, dv]``."""
+    _need_cuda(zq, zf, v, state, seqs)
+    n = zq.shape[0]
+    _, Hs, dk, dv = state.shape
+    if Hs != H or zq.shape[1] != H * dk or zf.shape != zq.shape or v.shape != (n, H * dv):
+        raise ValueError("projections do not match the state's shape")
+    stride = _rows2(zq)
+    if n > 1 and (zf.stride(0) != stride or v.stride(0) != stride):
+        raise ValueError("zq, zf and v must share a row stride")
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise TypeError("the recurrent state is contiguous fp32")
+    if seqs.dtype != torch.int32 or seqs.dim() != 2 or seqs.shape[1] != 4 or not seqs.is_contiguous():
+        raise ValueError("seqs must be contiguous int32 [n_seqs, 4]")
+    o = torch.empty((n, H, dv), dtype=torch.float32, device=zq.device)
+    rc = _lib_().b200_gated_scan(o.data_ptr(), zq.data_ptr(), zf.data_ptr(), v.data_ptr(), stride, f_bias.data_ptr(),
+                                 lower.data_ptr(), state.data_ptr(), seqs.data_ptr(), seqs.shape[0], H, dk, dv,
+                                 DTYPE_ID[zq.dtype], _stream())
+    _lib.check_mixers(rc, "b200_gated_scan")
+    return o
+
+
+def head_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """fp32 ``[..., dv]`` rows -> ``x * rsqrt(mean(x^2) + eps) * weight`` in the weight's dtype."""
+    _need_cuda(x, weight)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("x must be contiguous fp32")
+    dv = x.shape[-1]
+    out = torch.empty(x.shape, dtype=weight.dtype, device=x.device)
+    rc = _lib_().b200_head_rmsnorm(out.data_ptr(), x.data_ptr(), weight.data_ptr(), float(eps), x.numel() // dv, dv,
+                                   DTYPE_ID[weight.dtype], _stream())
+    _lib.check_mixers(rc, "b200_head_rmsnorm")
+    return out
+
+
+def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
+    _need_cuda(z, coef)
+    out = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+    rc = _lib_().b200_polynorm(out.data_ptr(), z.data_ptr(), _rows2(z), coef.data_ptr(), float(eps), z.shape[0],
+                               z.shape[1], DTYPE_ID[z.dtype], _stream())
+    _lib.check_mixers(rc, "b200_polynorm")
+    return out
+
+
+def sigmoid_topk(logits: torch.Tensor, top: int):
+    """fp32 ``[n, E]`` logits -> ``(ids int32 [n, top], weights fp32 [n, top])``; weights are sigmoid(logit)."""
+    _need_cuda(logits)
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or logits.dim() != 2:
+        raise ValueError("router logits are contiguous fp32 [n, E]")
+    n, E = logits.shape
+    ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    rc = _lib_().b200_sigmoid_topk(ids.data_ptr(), w.data_ptr(), logits.data_ptr(), n, E, int(top), _stream())
+    _lib.check_mixers(rc, "b200_sigmoid_topk")
+    return ids, w
+
+
+def scaled_gather(h: torch.Tensor, weights: torch.Tensor, src: torch.Tensor, top: int) -> torch.Tensor:
+    _need_cuda(h, weights, src)
+    if not h.is_contiguous() or src.dtype != torch.int64 or weights.dtype != torch.float32:
+        raise ValueError("h contiguous, src int64, weights fp32")
+    xs = torch.empty((src.numel(), h.shape[1]), dtype=h.dtype, device=h.device)
+    rc = _lib_().b200_scaled_gather(xs.data_ptr(), h.data_ptr(), weights.data_ptr(), src.data_ptr(), src.numel(), int(top),
+                                    h.shape[1], DTYPE_ID[h.dtype], _stream())
+    _lib.check_mixers(rc, "b200_scaled_gather")
+    return xs
+
+
+def clamped_glu(gu: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    _need_cuda(gu)
+    if not gu.is_contiguous() or gu.shape[1] % 2:
+        raise ValueError("gu must be contiguous [rows, 2*ff]")
+    ff = gu.shape[1] // 2
+    y = torch.empty((gu.shape[0], ff), dtype=gu.dtype, device=gu.device)
+    rc = _lib_().b200_clamped_glu(y.data_ptr(), gu.data_ptr(), gu.shape[0], ff, float(limit), float(alpha),
+                                  DTYPE_ID[gu.dtype], _stream())
+    _lib.check_mixers(rc, "b200_clamped_glu")
+    return y
+
+
+def expert_combine(ys: torch.Tensor, where: torch.Tensor, n_tok: int, top: int) -> torch.Tensor:
+    _need_cuda(ys, where)
+    if not ys.is_contiguous() or where.dtype != torch.int64 or where.numel() != n_tok * top:
+        raise ValueError("ys contiguous, where int64 [n_tok * top]")
+    out = torch.empty((n_tok, ys.shape[1]), dtype=torch.float32, device=ys.device)
+    rc = _lib_().b200_expert_combine(out.data_ptr(), ys.data_ptr(), where.data_ptr(), n_tok, int(top), ys.shape[1],
+                                     DTYPE_ID[ys.dtype], _stream())
+    _lib.check_mixers(rc, "b200_expert_combine")
+    return out

@@ -167,6 +167,62 @@ class PagedLayerKV:
     state: PagedBatchState
 
 
+@dataclass
+class RaggedBatchState:
+    """Device-side description of one PACKED step: row ``n`` of every activation is one token, the tokens of a
+    sequence are consecutive and in order, and sequences may bring any number of tokens (a prompt portion, or one
+    decoded token).  Shared by all layers of the step, like ``PagedBatchState`` is for fixed batches.
+
+    tok_pos        int32 [N]              position of each token in its sequence
+    slot_mapping   int64 [N]              pool slot of each token (block * block_size + offset)
+    block_tables   int32 [B, max_blocks]  pool blocks per live sequence of the step
+    scan_seqs      int32 [B, 4]           (first row, token count, recurrent-state slot, 1 if the sequence starts here)
+    spans          host list of (first row, token count, block-table row, tokens of the sequence before this step)
+    v_first        values the first value-mixing attention layer stored for this step's tokens (set by that layer)
+    pending_norm   the next sublayer's normed input when the previous layer already computed it in its epilogue
+    """
+
+    tok_pos: torch.Tensor
+    slot_mapping: torch.Tensor
+    block_tables: torch.Tensor
+    scan_seqs: torch.Tensor
+    spans: list
+    v_first: Optional[torch.Tensor] = None
+    pending_norm: Optional[torch.Tensor] = None
+    _tiles: Optional[dict] = None
+
+    def tiles_for(self, num_heads: int, num_kv_heads: int):
+        """``(tiles int32 [n, 3], tokens per tile at most)`` for an attention layer with this head layout: each
+        sequence's tokens cut into runs that one CTA serves, longest context first."""
+        from . import mixer_ops
+
+        cap = mixer_ops.attn_tile_tokens(1 << 20, num_heads, num_kv_heads)
+        if self._tiles is None:
+            self._tiles = {}
+        if cap not in self._tiles:
+            rows, most = [], 1
+            for first, count, table_row, past in self.spans:
+                for lo in range(0, count, cap):
+                    n = min(cap, count - lo)
+                    most = max(most, n)
+                    rows.append((past + lo + n, first + lo, n, table_row))
+            rows.sort(key=lambda r: -r[0])
+            t = torch.tensor([r[1:] for r in rows], dtype=torch.int32).reshape(-1, 3)
+            self._tiles[cap] = (t.to(self.tok_pos.device, non_blocking=True), most)
+        return self._tiles[cap]
+
+
+@dataclass
+class RaggedLayerCache:
+    """What a ragged layer expects in ``past_key_values[i]``: an attention layer's K / V pools (their row widths may
+    differ) or a recurrent layer's state tensor ``[slots, ...]``, plus the step's shared state."""
+
+    k_pool: Optional[torch.Tensor]
+    v_pool: Optional[torch.Tensor]
+    rstate: Optional[torch.Tensor]
+    state: RaggedBatchState
+
+
 class PagedLlamaDecoderLayer(nn.Module):
     """One Llama decoder layer; see the module docstring."""
 

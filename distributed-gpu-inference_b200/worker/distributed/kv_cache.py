@@ -142,11 +142,14 @@ class PagedKVCache:
         device: str = "cuda",
         dtype: torch.dtype = torch.float16,
         *,
+        value_head_dim: Optional[int] = None,
         _storage: Optional[Tuple[torch.Tensor, torch.Tensor]] = None,
     ):
         self.num_layers = num_layers
         self.num_heads = num_heads
         self.head_dim = head_dim
+        # addition: designs whose values are narrower / wider than their keys get a V pool of their own row width
+        self.value_head_dim = head_dim if value_head_dim is None else value_head_dim
         self.block_size = block_size
         self.max_blocks = max_blocks
         self.device = device
@@ -167,21 +170,22 @@ class PagedKVCache:
     # -- pool ---------------------------------------------------------------------------------------
     def _init_memory_pool(self, storage: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> None:
         shape = (self.max_blocks, self.num_heads, self.block_size, self.head_dim)
+        vshape = shape[:3] + (self.value_head_dim,)
         if storage is not None:
             k, v = storage
-            if tuple(k.shape) != shape or tuple(v.shape) != shape or not (k.is_contiguous() and v.is_contiguous()):
-                raise ValueError(f"backing storage must be two contiguous tensors of shape {shape}")
+            if tuple(k.shape) != shape or tuple(v.shape) != vshape or not (k.is_contiguous() and v.is_contiguous()):
+                raise ValueError(f"backing storage must be two contiguous tensors of shape {shape} / {vshape}")
             self._key_pool, self._value_pool = k, v
         else:
             self._key_pool = torch.zeros(shape, dtype=self.dtype, device=self.device)
-            self._value_pool = torch.zeros(shape, dtype=self.dtype, device=self.device)
+            self._value_pool = torch.zeros(vshape, dtype=self.dtype, device=self.device)
         self._free_blocks = [f"block_{i}" for i in range(self.max_blocks)]
         self._slot_of_id = {bid: i for i, bid in enumerate(self._free_blocks)}
 
     def _get_pool_memory_gb(self) -> float:
         if self._key_pool is None:
             return 0.0
-        return 2 * self._key_pool.numel() * self._key_pool.element_size() / (1024 ** 3)
+        return (self._key_pool.numel() + self._value_pool.numel()) * self._key_pool.element_size() / (1024 ** 3)
 
     @property
     def key_pool(self) -> torch.Tensor:
@@ -345,6 +349,7 @@ class KVCachePool:
         device: str = "cuda",
         dtype: torch.dtype = torch.float16,
         backing: Optional[torch.Tensor] = None,
+        layer_shapes: Optional[Sequence[Tuple[int, int, int]]] = None,
     ):
         self.num_layers = num_layers
         self.num_heads = num_heads
@@ -353,6 +358,19 @@ class KVCachePool:
         self.max_blocks_per_layer = max_blocks_per_layer
         self.device = device
         self.dtype = dtype
+        if layer_shapes is not None:
+            # addition: ``(kv heads, key size, value size)`` per layer, for models whose attention layers differ from
+            # one another or whose values are not as wide as their keys.  Every layer gets its own K and V tensor;
+            # block ids, slots and the allocation order are the same in all layers, as with the shared backing.
+            if backing is not None or len(layer_shapes) != num_layers:
+                raise ValueError("layer_shapes needs one (heads, key size, value size) per layer and no backing")
+            self.backing = None
+            self._layer_caches = [
+                PagedKVCache(num_layers=1, num_heads=h, head_dim=dk, block_size=block_size,
+                             max_blocks=max_blocks_per_layer, device=device, dtype=dtype, value_head_dim=dv)
+                for (h, dk, dv) in layer_shapes
+            ]
+            return
         shape = (num_layers, 2, max_blocks_per_layer, num_heads, block_size, head_dim)
         if backing is None:
             backing = torch.zeros(shape, dtype=dtype, device=device)
@@ -414,6 +432,32 @@ class KVCachePool:
             self._layer_caches[layer_idx].unpin(ids)
         return out
 
+    def extend_sequence(self, blocks: List[List[CacheBlock]], seq_len: int, prefix_hash: str = "") -> None:
+        """Grow a sequence's per-layer block lists (as ``allocate_sequence`` returned them) so that they hold
+        ``seq_len`` tokens — addition for engines that admit a request before its length is known and let it grow
+        step by step.  All layers grow together or, when the pool runs dry, none does (RuntimeError)."""
+        bs = self._layer_caches[0].block_size
+        need = (seq_len + bs - 1) // bs
+        grown: List[List[CacheBlock]] = []
+        for layer_idx, cache in enumerate(self._layer_caches):
+            more = need - len(blocks[layer_idx])
+            fresh = cache.allocate_blocks(layer_idx, more, prefix_hash) if more > 0 else []
+            if fresh is None:
+                fresh = []
+                for _ in range(more):
+                    blk = cache.allocate_block(layer_idx, prefix_hash)
+                    if blk is None:
+                        break
+                    cache.pin((blk.block_id,))
+                    fresh.append(blk)
+                cache.unpin(b.block_id for b in fresh)
+                if len(fresh) < more:
+                    self._free_sequence_blocks(grown + [fresh])
+                    raise RuntimeError(f"Failed to extend KV-Cache for layer {layer_idx}")
+            grown.append(fresh)
+        for layer_idx, fresh in enumerate(grown):
+            blocks[layer_idx].extend(fresh)
+
     def _free_sequence_blocks(self, blocks: List[List[CacheBlock]]) -> None:
         for layer_idx, layer_blocks in enumerate(blocks):
             cache = self._layer_caches[layer_idx]
@@ -436,6 +480,53 @@ class KVCachePool:
     def block_table(layer_blocks: Sequence[CacheBlock]) -> List[int]:
         """Pool slots of a sequence's blocks in allocation order — one row of the device block table."""
         return [b.slot for b in layer_blocks]
+
+
+class RecurrentStatePool:
+    """Fixed-size fp32 state per live sequence for layers that carry a recurrence instead of keys and values.
+
+    ``shapes[i]`` is the state shape of recurrent layer ``i`` (for a gated linear recurrence: ``(heads, key size,
+    value size)``); layer ``i`` owns one tensor ``[slots, *shapes[i]]``.  A sequence takes ONE slot number, valid in
+    every layer, at admission and gives it back at its end.  Slots are reused last-freed-first; a slot's content is
+    whatever its last owner left, so the first step of a sequence must start from zero (the scan kernels take a
+    ``fresh`` flag per sequence; ``reset`` zeroes a slot explicitly).  There is no reference counterpart: the
+    reference's caches hold keys and values only (worker/distributed/kv_cache.py:79-247).
+    """
+
+    def __init__(self, shapes: Sequence[Sequence[int]], slots: int, device: str = "cuda"):
+        self.slots = slots
+        self.shapes = [tuple(int(d) for d in s) for s in shapes]
+        self.device = device
+        self.states: List[torch.Tensor] = [torch.zeros((slots,) + s, dtype=torch.float32, device=device)
+                                           for s in self.shapes]
+        self._free: List[int] = list(range(slots - 1, -1, -1))
+        self._live: Dict[int, bool] = {}
+
+    def allocate(self) -> int:
+        if not self._free:
+            raise RuntimeError("no free recurrent-state slot")
+        slot = self._free.pop()
+        self._live[slot] = True
+        return slot
+
+    def free(self, slot: int) -> None:
+        if self._live.pop(slot, None) is None:
+            raise ValueError(f"state slot {slot} is not live")
+        self._free.append(slot)
+
+    def reset(self, slot: int) -> None:
+        for t in self.states:
+            t[slot].zero_()
+
+    def layer(self, idx: int) -> torch.Tensor:
+        return self.states[idx]
+
+    @property
+    def free_slots(self) -> int:
+        return len(self._free)
+
+    def get_total_memory_gb(self) -> float:
+        return sum(t.numel() * 4 for t in self.states) / (1024 ** 3)
 
 
 class DistributedKVCacheManager:
