@@ -108,6 +108,8 @@ class RaggedStepEngine:
         req = self.requests.pop(rid)
         for pool, blocks in zip(self.kv_pools, req.blocks):
             if pool is not None:
+                for li, layer_blocks in enumerate(blocks):
+                    pool.layer(li).unpin(b.block_id for b in layer_blocks)
                 pool.free_sequence(blocks)
         for sp in self.state_pools:
             if sp is not None:
@@ -130,7 +132,8 @@ class RaggedStepEngine:
             if pool is None:
                 continue
             pool.extend_sequence(blocks, new_len)
-            for layer_blocks in blocks:
+            for li, layer_blocks in enumerate(blocks):
+                pool.layer(li).pin(b.block_id for b in layer_blocks[have:])   # a live request's pages are not evictable
                 got = [b.slot for b in layer_blocks[have:]]
                 if row is None:
                     row = got
@@ -151,6 +154,22 @@ class RaggedStepEngine:
         pos_l: List[np.ndarray] = []
         slot_l: List[np.ndarray] = []
         spans, scans, wanted, rows = [], [], [], []
+        # refuse the whole step before touching anything when its pages or slots do not fit
+        new_blocks, new_seqs, seen = 0, 0, set()
+        for rid, toks, _want in entries:
+            if len(toks) == 0:
+                continue
+            if rid in seen:
+                raise ValueError(f"request {rid!r} appears twice in one step")
+            seen.add(rid)
+            req = self.requests.get(rid)
+            have, length = (len(req.table), req.length) if req is not None else (0, 0)
+            new_seqs += req is None
+            new_blocks += max(0, (length + len(toks) + bs - 1) // bs - have)
+        if new_seqs > self.free_slots:
+            raise RuntimeError(f"no free sequence slot: the step admits {new_seqs}, {self.free_slots} free")
+        if new_blocks > self.free_blocks:
+            raise RuntimeError(f"KV pages exhausted: the step needs {new_blocks} more, {self.free_blocks} free")
         for rid, toks, want in entries:
             n = len(toks)
             if n == 0:

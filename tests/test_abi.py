@@ -12,12 +12,31 @@ from dgi_b200 import _lib, ops
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
-    names = set()
-    for path in glob.glob(os.path.join(ROOT, "include", "*.h")):
-        text = re.sub(r"/\*.*?\*/", "", open(path).read(), flags=re.S)
-        names.update(re.findall(r"\b(b200_\w+)\s*\(", text))
-    return sorted(names)
+def declared_symbols(header="b200_kv.h"):
+    """Functions a header of include/ declares; each header is the surface of one shared library."""
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", header)).read(), flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_\w+)\s*\(", text)))
+
+
+def test_every_header_has_a_loader():
+    assert sorted(os.path.basename(p) for p in glob.glob(os.path.join(ROOT, "include", "*.h"))) == \
+        ["b200_kv.h", "b200_mixers.h"]
+
+
+def test_mixers_library_matches_its_header():
+    assert sorted(_lib.MIXER_SIGNATURES) == declared_symbols("b200_mixers.h")
+    lib = _lib.load_mixers()     # builds the library when the checkout has none
+    assert lib.b200_mixers_abi_version() == 1
+    for name in declared_symbols("b200_mixers.h"):
+        assert hasattr(lib, name), f"{name} declared in include/b200_mixers.h but not exported"
+    # host-side helper: tokens of a portion one CTA serves (8 warps x 4 rows over the head group)
+    assert lib.b200_biased_attn_tile_tokens(1000, 4, 1) == 8
+    assert lib.b200_biased_attn_tile_tokens(1000, 8, 8) == 32
+    assert lib.b200_biased_attn_tile_tokens(1, 4, 1) == 1
+    rc = lib.b200_polynorm(None, None, 0, None, 1e-6, 4, 8, 7, None)  # dtype 7
+    assert rc == -1 and b"null pointer" in lib.b200_mixers_last_error()
+    rc = lib.b200_gated_scan(None, None, None, None, 0, None, None, None, None, 1, 0, 4, 4, 2, None)
+    assert rc == -1 and b"bad sizes" in lib.b200_mixers_last_error()
 
 
 def test_header_declares_the_expected_surface():
