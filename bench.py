@@ -678,8 +678,17 @@ def main():
                          "weak-scaled 8B pipeline)")
     ap.add_argument("--no-parity", action="store_true", help="multi-GPU: skip the token checks of the run")
     ap.add_argument("--no-vocab-parallel-head", action="store_true",
-                    help="multi-GPU: keep lm_head + argmax on the last stage (the round-1 arrangement)")
+                    help="multi-GPU: keep lm_head + argmax on the last stage (instead of the vocabulary-parallel head)")
+    ap.add_argument("--compare", default="", choices=["", "petipel"],
+                    help="petipel: prompt-pass and decode throughput of the Petipel model class (ragged step engine) beside "
+                         "a Llama shape of equal size, with per-kernel times; prints its own JSON line")
+    ap.add_argument("--compare-sizes", default="", help="with --compare: comma-separated subset of w1024,w2048,w4096")
     args = ap.parse_args()
+    if args.compare == "petipel":
+        from dgi_b200.bench_ragged import run as run_compare
+
+        run_compare(args, measured_peaks, ClockSampler)
+        return
     if args.warmup < 3:
         args.warmup = 3
     rank = int(os.environ.get("RANK", "0"))

@@ -1,0 +1,197 @@
+"""``bench.py --compare petipel``: prompt-pass and decode throughput of the Petipel model class on the ragged step
+engine beside a Llama-shaped model of equal width, depth and head layout on the paged decode engine, plus the time
+of every mixer kernel of one prompt step and one decode step against its memory / math floor.
+
+Random weights, synthetic token ids; bf16.  Timed with CUDA events on the launching stream after warm-up; the
+inputs of a step (activations, weights, KV of all sequences) exceed L2 at the two larger sizes and the report says
+so per size.  One JSON line on stdout; the default workload and contract of bench.py are untouched.
+"""
+from __future__ import annotations
+
+import json
+import math
+import statistics
+from typing import Any, Dict, List
+
+import torch
+
+SIZES = {
+    # width, query heads, kv heads, head size; recurrent heads and their key / value sizes; feed-forward sizes
+    "w1024": dict(width=1024, heads=8, kv=2, dk=128, dv=128, rheads=8, rdk=64, rdv=128, ff=4096, experts=8, eff=1024, top=2),
+    "w2048": dict(width=2048, heads=16, kv=4, dk=128, dv=128, rheads=16, rdk=64, rdv=128, ff=8192, experts=8, eff=2048, top=2),
+    "w4096": dict(width=4096, heads=32, kv=8, dk=128, dv=128, rheads=32, rdk=64, rdv=128, ff=14336, experts=8, eff=3584, top=2),
+}
+LAYERS = 4
+VOCAB = 32000
+
+
+def petipel_config(s: Dict[str, int]) -> Dict[str, Any]:
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv"], "dim": s["dk"], "vdim": s["dv"],
+                                          "scale": 1.0 / math.sqrt(s["dk"]), "bias_max": 4096, "v_mix": True,
+                                          "q_temp": {"coef": 0.1, "every": 512}}}
+    rec = {"type": "hgrn2", "mixer": {"heads": s["rheads"], "dim": s["rdk"], "vdim": s["rdv"]}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": s["eff"], "limit": 7.0}, "router": {"experts": s["experts"], "top": s["top"]}}
+    layers = []
+    for i in range(LAYERS):
+        layer = dict(rec if i % 2 == 0 else att)
+        layer["mlp"] = dense if i % 4 < 2 else moe
+        layers.append(layer)
+    return {"architecture": "Petipel", "width": s["width"], "vocab": VOCAB, "residual_mult": 0.5,
+            "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def _events_ms(pairs) -> float:
+    return sum(a.elapsed_time(b) for a, b in pairs)
+
+
+def _time_steps(fn, steps: int, warmup: int) -> float:
+    """Median milliseconds of ``fn()`` over ``steps`` runs, CUDA events on the current stream."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(steps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        out.append(a.elapsed_time(b))
+    return statistics.median(out)
+
+
+def run(args, measured_peaks, ClockSampler) -> None:
+    from . import mixer_ops, ops
+    from . import petipel_layer as P
+    from .engine import PagedDecodeEngine
+    from .ragged_engine import RaggedStepEngine
+    from .testing import LlamaShapeConfig
+    from .worker.distributed.model_shard import ModelShard
+
+    dev = "cuda:0"
+    peaks, how = measured_peaks()
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    steps, warmup = max(3, args.steps), max(3, args.warmup)
+    B, Pn, ctx = 8, 2048, 2048          # prompt pass: 8 x 2048 tokens in one step; decode: 64 sequences at 2k context
+    Bd = 64
+    g = torch.Generator().manual_seed(0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    report: Dict[str, Any] = {}
+    for name, s in SIZES.items():
+        if args.compare_sizes and name not in args.compare_sizes.split(","):
+            continue
+        row: Dict[str, Any] = {}
+        # ---- Petipel on the ragged step engine -----------------------------------------------------------------
+        raw = petipel_config(s)
+        cfg = P.PetipelConfig.from_dict(raw)
+        shards = P.build_shards(cfg, P.random_checkpoint(cfg, seed=0), [(0, LAYERS)], dev, torch.bfloat16)
+        eng = RaggedStepEngine(shards, max_tokens=Bd * (ctx + 64), max_seqs=Bd, fp32_logits=False)
+        prompts = torch.randint(0, VOCAB, (Bd, ctx), generator=g).tolist()
+
+        def prompt_step():
+            eng.step([(i, prompts[i][:Pn], [Pn - 1]) for i in range(B)])
+            for i in range(B):
+                eng.finish(i)
+
+        ms = _time_steps(prompt_step, steps, warmup)
+        row["petipel_prefill_tok_s"] = round(B * Pn / ms * 1e3)
+        mixer_ops.EVENTS = []
+        prompt_step()
+        torch.cuda.synchronize()
+        ev_prompt, mixer_ops.EVENTS = mixer_ops.EVENTS, None
+        for i in range(0, Bd, B):        # fill 64 sequences to the decode context
+            eng.step([(j, prompts[j], []) for j in range(i, i + B)])
+        nxt = [[1] for _ in range(Bd)]
+
+        def decode_step():
+            eng.step([(j, nxt[j], [0]) for j in range(Bd)])
+
+        ms = _time_steps(decode_step, min(steps, 32), warmup)
+        row["petipel_decode_tok_s"] = round(Bd / ms * 1e3)
+        mixer_ops.EVENTS = []
+        decode_step()
+        torch.cuda.synchronize()
+        ev_decode, mixer_ops.EVENTS = mixer_ops.EVENTS, None
+        eng.release()
+        row["kernels"] = _kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx + warmup + min(steps, 32), hbm, tf)
+        del eng, shards
+        torch.cuda.empty_cache()
+        # ---- Llama shape of equal width / depth / heads on the paged engine ----------------------------------------
+        lcfg = LlamaShapeConfig(hidden_size=s["width"], num_attention_heads=s["heads"], num_key_value_heads=s["kv"],
+                                head_dim=s["dk"], intermediate_size=s["ff"], vocab_size=VOCAB, num_hidden_layers=LAYERS)
+        shard = ModelShard.from_config(lcfg, 0, LAYERS, device=dev, dtype=torch.bfloat16, seed=0)
+        leng = PagedDecodeEngine([shard], max_batch=Bd, max_seq_len=ctx + 64, fuse_projections=True)
+        ids = torch.tensor(prompts, dtype=torch.int64)
+
+        def llama_prompt():
+            leng.allocate(B, Pn + 1)
+            leng.prefill(ids[:B, :Pn])
+
+        ms = _time_steps(llama_prompt, steps, warmup)
+        row["llama_prefill_tok_s"] = round(B * Pn / ms * 1e3)
+        ops.ATTN_EVENTS = []
+        llama_prompt()
+        torch.cuda.synchronize()
+        ops.ATTN_EVENTS = None
+        leng.allocate(Bd, ctx + 64)
+        leng.prefill(ids)
+        leng.ids_buf[:Bd, 0].fill_(1)
+        ms = _time_steps(leng.decode_step_device, min(steps, 32), warmup)
+        row["llama_decode_tok_s"] = round(Bd / ms * 1e3)
+        leng.use_cuda_graph = False
+        ops.ATTN_EVENTS = []
+        leng.decode_step_device()
+        torch.cuda.synchronize()
+        pairs, ops.ATTN_EVENTS = ops.ATTN_EVENTS, None
+        if pairs:
+            t = _events_ms(pairs) / len(pairs) * 1e-3
+            kv_bytes = Bd * (ctx + 40) * s["kv"] * 2 * s["dk"] * 2
+            row["llama_decode_attention"] = {"us": round(t * 1e6, 1), "of_copy_peak": round(kv_bytes / t / hbm, 3)}
+        leng.release()
+        del leng, shard
+        torch.cuda.empty_cache()
+        row["inputs_exceed_l2"] = bool(Bd * ctx * s["kv"] * (s["dk"] + s["dv"]) * 2 > 126e6)
+        report[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"bench": "petipel_vs_llama", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                      "layers": LAYERS, "prompt_step": f"{B} x {Pn} tokens", "decode_step": f"{Bd} sequences at {ctx}",
+                      "peaks": how, "sizes": report, "clocks": clocks}), flush=True)
+
+
+def _kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> Dict[str, Any]:
+    """Per kernel: mean microseconds in the prompt step and in the decode step, and the fraction of the floor
+    max(bytes / copy peak, flops / bf16 peak) for the ones whose traffic is easy to state."""
+    out: Dict[str, Any] = {}
+    W, H, G, dk, dv = s["width"], s["heads"], s["kv"], s["dk"], s["dv"]
+    RH, rdk, rdv = s["rheads"], s["rdk"], s["rdv"]
+    for phase, events, n_tok, past in (("prompt", ev_prompt, B * Pn, 0), ("decode", ev_decode, Bd, ctx)):
+        by: Dict[str, List[float]] = {}
+        for name, a, b in events:
+            by.setdefault(name, []).append(a.elapsed_time(b) * 1e-3)
+        per_seq = n_tok // (B if phase == "prompt" else Bd)
+        n_seq = n_tok // per_seq
+        floors = {
+            "offset_rmsnorm": (n_tok * W * 6, 0),
+            "postnorm_residual": (n_tok * W * (4 + 4 + 2 + 2), 0),
+            "value_prep_append": (n_tok * G * (dk + dv) * 2 * 2 + n_tok * G * dv * 2, 0),
+            "biased_paged_attention": (n_seq * (past + per_seq) * G * (dk + dv) * 2 + n_tok * H * (dk + dv) * 2,
+                                       n_seq * H * 2 * (dk + dv) * (per_seq * past + per_seq * (per_seq + 1) // 2)),
+            "gated_scan": (n_tok * RH * (2 * rdk + rdv) * 2 + n_tok * RH * rdv * 4 + 2 * n_seq * RH * rdk * rdv * 4, 0),
+            "head_rmsnorm": (n_tok * RH * rdv * 6, 0),
+            "polynorm": (n_tok * s["ff"] * 4, 0),
+            "clamped_glu": (n_tok * s["top"] * s["eff"] * 6, 0),
+            "scaled_gather": (n_tok * s["top"] * W * 4, 0),
+            "expert_combine": (n_tok * s["top"] * W * 2 + n_tok * W * 4, 0),
+        }
+        for name, ts in by.items():
+            t = statistics.mean(ts)
+            entry = {"us": round(t * 1e6, 1), "calls": len(ts)}
+            if name in floors:
+                nbytes, flops = floors[name]
+                floor = max(nbytes / hbm, flops / tf)
+                entry["of_floor"] = round(floor / t, 3)
+                entry["bound"] = "math" if flops / tf > nbytes / hbm else "memory"
+            out.setdefault(phase, {})[name] = entry
+    return out

@@ -159,13 +159,15 @@ struct AttnTile {
 constexpr int kAttnWarps = 8;
 constexpr int kKeyTile = 32;
 
-template <typename T, int RW, int DVL>
+template <typename T, int RW, int DVL, int NCH>
 __global__ void __launch_bounds__(kAttnWarps * 32)
 biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stride, const T* __restrict__ gate,
                          int64_t gate_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                          const int32_t* __restrict__ block_tables, int table_stride, const AttnTile* __restrict__ tiles,
                          const int32_t* __restrict__ tok_pos, const float* __restrict__ bias_lut, int lut_len,
                          float scale, float temp_coef, int temp_every, int H, int G, int dk, int dv, int block_size) {
+  // NCH > 0: K / V rows are fetched as 16-byte chunks, NCH per thread, into registers one key tile AHEAD of the
+  // tile being computed (needs dk and dv to be multiples of 16 bytes).  NCH == 0: element-wise loads, any sizes.
   extern __shared__ float smem[];
   const int dkp = (dk + 3) & ~3;            // padded row length of K / q rows (multiple of 4 floats)
   const int ks = dkp + 4;                   // K row stride: 16-byte aligned and conflict-free for 128-bit reads
@@ -206,30 +208,84 @@ biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q
     for (int c = 0; c < DVL; ++c) acc[r][c] = 0.f;
   }
 
+  constexpr int VN = 16 / sizeof(T);
+  constexpr int NR = NCH > 0 ? NCH : 1;
+  const int kc = dk / VN, vc = dv / VN;               // chunks per K / V row
+  const int n_chunks = kKeyTile * (kc + vc);
+  int4 regs[NR];
+  auto chunk_of = [&](int c, bool& isv, int& j, int& e) {
+    isv = c >= kKeyTile * kc;
+    const int cc = isv ? c - kKeyTile * kc : c;
+    const int per = isv ? vc : kc;
+    j = cc / per;
+    e = (cc - j * per) * VN;
+  };
+  auto prefetch = [&](int j0) {
+    const int n_keys = min(kKeyTile, pos_last + 1 - j0);
+#pragma unroll
+    for (int u = 0; u < NR; ++u) {
+      const int c = threadIdx.x + u * kAttnWarps * 32;
+      regs[u] = make_int4(0, 0, 0, 0);
+      if (c < n_chunks) {
+        bool isv;
+        int j, e;
+        chunk_of(c, isv, j, e);
+        if (j < n_keys) {
+          const int key = j0 + j;
+          const int64_t row = (static_cast<int64_t>(table[key / block_size]) * G + g) * block_size + key % block_size;
+          regs[u] = *reinterpret_cast<const int4*>(isv ? v_pool + row * dv + e : k_pool + row * dk + e);
+        }
+      }
+    }
+  };
+  auto commit = [&]() {
+#pragma unroll
+    for (int u = 0; u < NR; ++u) {
+      const int c = threadIdx.x + u * kAttnWarps * 32;
+      if (c < n_chunks) {
+        bool isv;
+        int j, e;
+        chunk_of(c, isv, j, e);
+        const T* el = reinterpret_cast<const T*>(&regs[u]);
+        float* dst = isv ? v_s + j * dv + e : k_s + j * ks + e;
+#pragma unroll
+        for (int i = 0; i < VN; ++i) dst[i] = Cvt<T>::to_f32(el[i]);
+      }
+    }
+  };
+  if constexpr (NCH > 0) prefetch(0);
+
   for (int j0 = 0; j0 <= pos_last; j0 += kKeyTile) {
     __syncthreads();  // previous tile fully consumed (and q_s written, first time round)
     const int n_keys = min(kKeyTile, pos_last + 1 - j0);
-    for (int i = threadIdx.x; i < kKeyTile * dkp; i += blockDim.x) {
-      const int j = i / dkp, d = i - j * dkp;
-      float f = 0.f;
-      if (j < n_keys && d < dk) {
-        const int key = j0 + j;
-        const int64_t blk = table[key / block_size];
-        f = Cvt<T>::to_f32(k_pool[((blk * G + g) * block_size + key % block_size) * dk + d]);
+    if constexpr (NCH > 0) {
+      commit();
+    } else {
+      for (int i = threadIdx.x; i < kKeyTile * dkp; i += blockDim.x) {
+        const int j = i / dkp, d = i - j * dkp;
+        float f = 0.f;
+        if (j < n_keys && d < dk) {
+          const int key = j0 + j;
+          const int64_t blk = table[key / block_size];
+          f = Cvt<T>::to_f32(k_pool[((blk * G + g) * block_size + key % block_size) * dk + d]);
+        }
+        k_s[j * ks + d] = f;
       }
-      k_s[j * ks + d] = f;
-    }
-    for (int i = threadIdx.x; i < kKeyTile * dv; i += blockDim.x) {
-      const int j = i / dv, c = i - j * dv;
-      float f = 0.f;
-      if (j < n_keys) {
-        const int key = j0 + j;
-        const int64_t blk = table[key / block_size];
-        f = Cvt<T>::to_f32(v_pool[((blk * G + g) * block_size + key % block_size) * dv + c]);
+      for (int i = threadIdx.x; i < kKeyTile * dv; i += blockDim.x) {
+        const int j = i / dv, c = i - j * dv;
+        float f = 0.f;
+        if (j < n_keys) {
+          const int key = j0 + j;
+          const int64_t blk = table[key / block_size];
+          f = Cvt<T>::to_f32(v_pool[((blk * G + g) * block_size + key % block_size) * dv + c]);
+        }
+        v_s[i] = f;
       }
-      v_s[i] = f;
     }
     __syncthreads();
+    if constexpr (NCH > 0) {
+      if (j0 + kKeyTile <= pos_last) prefetch(j0 + kKeyTile);
+    }
 
     // scores: lane = key of the tile
     float s[RW];
@@ -312,67 +368,97 @@ struct ScanSeq {
   int fresh;  // 1: the sequence starts here, the state is zero
 };
 
+constexpr int kScanCols = 32;   // value columns per CTA (fixed, so the row-sum order never depends on the batch)
+constexpr int kScanRG = 256 / kScanCols;
+constexpr int kScanPF = 4;      // input elements per thread and token: 2 dk + 32 <= 1024
+
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_scan_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, const T* __restrict__ zf, const T* __restrict__ v,
                   int64_t in_stride, const T* __restrict__ f_bias, const T* __restrict__ lower, float* __restrict__ state,
-                  const ScanSeq* __restrict__ seqs, int H, int dk, int dv, int TC) {
+                  const ScanSeq* __restrict__ seqs, int H, int dk, int dv) {
   extern __shared__ float smem[];
   const ScanSeq sq = seqs[blockIdx.x];
   const int h = blockIdx.y;
-  const int RG = blockDim.x / TC;
-  const int c0 = threadIdx.x % TC, rg = threadIdx.x / TC;
-  float* S = smem;                         // [dk][dv]
-  float* in_s = S + dk * dv;               // 2 x (q[dk], f[dk], v[dv])
-  const int in_len = 2 * dk + dv;
-  float* part = in_s + 2 * in_len;         // [RG][dv]
+  const int col0 = blockIdx.z * kScanCols;
+  const int ncol = min(kScanCols, dv - col0);
+  const int c = threadIdx.x % kScanCols, rg = threadIdx.x / kScanCols;
+  float* S = smem;                              // [dk][kScanCols]
+  float* in_s = S + dk * kScanCols;             // 2 x (q[dk], f[dk], v[kScanCols])
+  const int in_len = 2 * dk + kScanCols;
+  float* part = in_s + 2 * in_len;              // [kScanRG][kScanCols]
   float* st = state + (static_cast<int64_t>(sq.slot) * H + h) * dk * dv;
-  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) S[i] = sq.fresh ? 0.f : st[i];
-
-  auto fetch = [&](int t, float* dst) {
+  for (int i = threadIdx.x; i < dk * kScanCols; i += blockDim.x) {
+    const int r = i / kScanCols, cc = i - r * kScanCols;
+    S[i] = (sq.fresh || cc >= ncol) ? 0.f : st[r * dv + col0 + cc];
+  }
+  // element i of a token's inputs is always handled by thread i % 256: its bias / bound are loaded once
+  float bias_r[kScanPF], low_r[kScanPF];
+#pragma unroll
+  for (int u = 0; u < kScanPF; ++u) {
+    const int i = threadIdx.x + u * 256;
+    bias_r[u] = low_r[u] = 0.f;
+    if (i >= dk && i < 2 * dk) {
+      bias_r[u] = Cvt<T>::to_f32(f_bias[h * dk + i - dk]);
+      low_r[u] = Cvt<T>::to_f32(lower[h * dk + i - dk]);
+    }
+  }
+  T raw[kScanPF];
+  auto fetch = [&](int t) {     // raw loads only: nothing waits for them until `commit`
     const int64_t row = static_cast<int64_t>(sq.tok0 + t) * in_stride;
-    for (int i = threadIdx.x; i < in_len; i += blockDim.x) {
-      float r;
-      if (i < dk) {
-        const float z = Cvt<T>::to_f32(zq[row + h * dk + i]);
-        r = z * sigmoidf_(z);
-      } else if (i < 2 * dk) {
-        const int d = h * dk + (i - dk);
-        const float lo = Cvt<T>::to_f32(lower[d]);
-        r = lo + (1.0f - lo) * sigmoidf_(Cvt<T>::to_f32(zf[row + d]) + Cvt<T>::to_f32(f_bias[d]));
-      } else {
-        r = Cvt<T>::to_f32(v[row + h * dv + (i - 2 * dk)]);
-      }
-      dst[i] = r;
+#pragma unroll
+    for (int u = 0; u < kScanPF; ++u) {
+      const int i = threadIdx.x + u * 256;
+      raw[u] = Cvt<T>::from_f32(0.f);
+      if (i < dk) raw[u] = zq[row + h * dk + i];
+      else if (i < 2 * dk) raw[u] = zf[row + h * dk + i - dk];
+      else if (i < 2 * dk + ncol) raw[u] = v[row + h * dv + col0 + i - 2 * dk];
     }
   };
-  fetch(0, in_s);
+  auto commit = [&](float* dst) {
+#pragma unroll
+    for (int u = 0; u < kScanPF; ++u) {
+      const int i = threadIdx.x + u * 256;
+      if (i < in_len) {
+        const float z = Cvt<T>::to_f32(raw[u]);
+        float r = z;                                              // value column
+        if (i < dk) r = z * sigmoidf_(z);                         // q = silu(zq)
+        else if (i < 2 * dk) r = low_r[u] + (1.0f - low_r[u]) * sigmoidf_(z + bias_r[u]);
+        dst[i] = r;
+      }
+    }
+  };
+  fetch(0);
+  commit(in_s);
   __syncthreads();
   for (int t = 0; t < sq.count; ++t) {
     const float* cur = in_s + (t & 1) * in_len;
-    if (t + 1 < sq.count) fetch(t + 1, in_s + ((t + 1) & 1) * in_len);
-    for (int c = c0; c < dv; c += TC) {
+    if (t + 1 < sq.count) fetch(t + 1);
+    {
       const float vc = cur[2 * dk + c];
       float sum = 0.f;
-      for (int i = rg; i < dk; i += RG) {
+      for (int i = rg; i < dk; i += kScanRG) {
         const float f = cur[dk + i];
-        const float s_new = f * S[i * dv + c] + (1.0f - f) * vc;
-        S[i * dv + c] = s_new;
+        const float s_new = f * S[i * kScanCols + c] + (1.0f - f) * vc;
+        S[i * kScanCols + c] = s_new;
         sum = fmaf(s_new, cur[i], sum);
       }
-      part[rg * dv + c] = sum;
+      part[rg * kScanCols + c] = sum;
     }
+    if (t + 1 < sq.count) commit(in_s + ((t + 1) & 1) * in_len);
     __syncthreads();
-    if (rg == 0) {
-      for (int c = c0; c < dv; c += TC) {
-        float o = 0.f;
-        for (int r = 0; r < RG; ++r) o += part[r * dv + c];
-        o_raw[(static_cast<int64_t>(sq.tok0 + t) * H + h) * dv + c] = o;
-      }
+    if (rg == 0 && c < ncol) {
+      float o = 0.f;
+#pragma unroll
+      for (int r = 0; r < kScanRG; ++r) o += part[r * kScanCols + c];
+      o_raw[(static_cast<int64_t>(sq.tok0 + t) * H + h) * dv + col0 + c] = o;
     }
     __syncthreads();
   }
-  for (int i = threadIdx.x; i < dk * dv; i += blockDim.x) st[i] = S[i];
+  for (int i = threadIdx.x; i < dk * kScanCols; i += blockDim.x) {
+    const int r = i / kScanCols, cc = i - r * kScanCols;
+    if (cc < ncol) st[r * dv + col0 + cc] = S[i];
+  }
 }
 
 // per-head weighted RMS norm of fp32 rows [rows, dv] -> T; one warp per row
@@ -597,15 +683,26 @@ int b200_biased_paged_attn(void* out, const void* q, int64_t q_stride, const voi
           block_size);
     };
     const int dvl = (dv + 31) / 32;
+    // 16-byte chunk loads with a one-tile register prefetch when rows are multiples of 16 bytes and a tile's chunks
+    // fit 4 (or 8) per thread; element-wise loads otherwise
+    constexpr int VN = 16 / static_cast<int>(sizeof(T));
+    const bool vec = dk % VN == 0 && dv % VN == 0 && aligned16(k_pool) && aligned16(v_pool);
+    const int per_thread = vec ? (kKeyTile * (dk / VN + dv / VN) + kAttnWarps * 32 - 1) / (kAttnWarps * 32) : 0;
+    const int nch = !vec || per_thread > 8 ? 0 : (per_thread <= 4 ? 4 : 8);
+#define B200_ATTN_DV(RW_, NCH_)                                              \
+  if (dvl <= 1) launch(biased_paged_attn_kernel<T, RW_, 1, NCH_>);           \
+  else if (dvl <= 2) launch(biased_paged_attn_kernel<T, RW_, 2, NCH_>);      \
+  else if (dvl <= 4) launch(biased_paged_attn_kernel<T, RW_, 4, NCH_>);      \
+  else launch(biased_paged_attn_kernel<T, RW_, 8, NCH_>);
 #define B200_ATTN_CASE(RW_)                                                  \
-  if (dvl <= 1) launch(biased_paged_attn_kernel<T, RW_, 1>);                 \
-  else if (dvl <= 2) launch(biased_paged_attn_kernel<T, RW_, 2>);            \
-  else if (dvl <= 4) launch(biased_paged_attn_kernel<T, RW_, 4>);            \
-  else launch(biased_paged_attn_kernel<T, RW_, 8>);
+  if (nch == 4) { B200_ATTN_DV(RW_, 4) }                                     \
+  else if (nch == 8) { B200_ATTN_DV(RW_, 8) }                                \
+  else { B200_ATTN_DV(RW_, 0) }
     if (rw <= 1) { B200_ATTN_CASE(1) }
     else if (rw <= 2) { B200_ATTN_CASE(2) }
     else { B200_ATTN_CASE(4) }
 #undef B200_ATTN_CASE
+#undef B200_ATTN_DV
     return check_launch("b200_biased_paged_attn");
   });
 }
@@ -616,13 +713,10 @@ int b200_gated_scan(float* o_raw, const void* zq, const void* zf, const void* v,
   if (n_seqs < 0 || H <= 0 || dk <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_gated_scan: bad sizes");
   if (n_seqs == 0) return 0;
   if (!o_raw || !zq || !zf || !v || !f_bias || !lower || !state || !seqs) return fail(B200_EINVAL, "b200_gated_scan: null pointer");
-  int TC = 1;
-  while (TC < dv && TC < 256) TC <<= 1;
-  const int RG = 256 / TC;
-  const size_t smem = sizeof(float) * (static_cast<size_t>(dk) * dv + 2 * (2 * static_cast<size_t>(dk) + dv) +
-                                       static_cast<size_t>(RG) * dv);
-  if (smem > 200 * 1024) return fail(B200_ESHAPE, "b200_gated_scan: state %d x %d does not fit shared memory", dk, dv);
-  const dim3 grid(n_seqs, H);
+  if (2 * dk + kScanCols > kScanPF * 256) return fail(B200_ESHAPE, "b200_gated_scan: key size %d beyond %d", dk, (kScanPF * 256 - kScanCols) / 2);
+  const size_t smem = sizeof(float) * (static_cast<size_t>(dk) * kScanCols + 2 * (2 * static_cast<size_t>(dk) + kScanCols) +
+                                       static_cast<size_t>(kScanRG) * kScanCols);
+  const dim3 grid(n_seqs, H, (dv + kScanCols - 1) / kScanCols);
   return mixer_by_dtype(dtype, "b200_gated_scan", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
     auto kern = gated_scan_kernel<T>;
@@ -630,7 +724,7 @@ int b200_gated_scan(float* o_raw, const void* zq, const void* zf, const void* v,
     kern<<<grid, 256, smem, static_cast<cudaStream_t>(stream)>>>(
         o_raw, static_cast<const T*>(zq), static_cast<const T*>(zf), static_cast<const T*>(v), in_stride,
         static_cast<const T*>(f_bias), static_cast<const T*>(lower), state, reinterpret_cast<const ScanSeq*>(seqs), H, dk,
-        dv, TC);
+        dv);
     return check_launch("b200_gated_scan");
   });
 }

@@ -13,6 +13,28 @@ from . import _lib
 from .ops import DTYPE_ID, _need_cuda, _stream
 
 
+# benchmark instrumentation: when set to a list, every op appends (name, start event, end event) recorded on the
+# launching stream around its C-ABI call
+EVENTS: Optional[list] = None
+
+
+def _timed(fn):
+    import functools
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        if EVENTS is None:
+            return fn(*args, **kwargs)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = fn(*args, **kwargs)
+        b.record()
+        EVENTS.append((fn.__name__, a, b))
+        return out
+
+    return wrapper
+
+
 def _lib_():
     return _lib.load_mixers()
 
@@ -28,6 +50,7 @@ def _rows2(x: torch.Tensor) -> int:
     return x.stride(0) if x.shape[0] > 1 else max(x.stride(0), x.shape[1])
 
 
+@_timed
 def offset_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """``x * rsqrt(mean(x^2) + eps) * (1 + weight)``: fp32 ``[rows, width]`` in, the weight's dtype out."""
     _need_cuda(x, weight)
@@ -40,6 +63,7 @@ def offset_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.T
     return out
 
 
+@_timed
 def postnorm_residual(x: torch.Tensor, y: torch.Tensor, w_post: torch.Tensor, mult: float, eps: float,
                       w_next: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
     """In place ``x += mult * offset_norm(y; w_post)`` (fp32); returns ``offset_norm(x; w_next)`` in the weights'
@@ -57,6 +81,7 @@ def postnorm_residual(x: torch.Tensor, y: torch.Tensor, w_post: torch.Tensor, mu
     return out
 
 
+@_timed
 def value_prep_append(k: torch.Tensor, v: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                       slot_mapping: torch.Tensor, eps: float, v_prev: Optional[torch.Tensor] = None, lam: float = 0.0,
                       v_keep: Optional[torch.Tensor] = None) -> None:
@@ -83,6 +108,7 @@ def attn_tile_tokens(n_tokens: int, H: int, G: int) -> int:
     return int(_lib_().b200_biased_attn_tile_tokens(int(n_tokens), H, G))
 
 
+@_timed
 def biased_paged_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: torch.Tensor,
                            block_tables: torch.Tensor, tiles: torch.Tensor, max_tile_tokens: int, tok_pos: torch.Tensor,
                            bias_lut: torch.Tensor, scale: float, temp_coef: float, temp_every: int, H: int) -> torch.Tensor:
@@ -111,6 +137,7 @@ def biased_paged_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pool
     return out
 
 
+@_timed
 def gated_scan(zq: torch.Tensor, zf: torch.Tensor, v: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor,
                state: torch.Tensor, seqs: torch.Tensor, H: int) -> torch.Tensor:
     """Gated linear recurrence over each sequence's tokens; ``state`` fp32 ``[slots, H, dk, dv]`` is read (unless the
@@ -136,6 +163,7 @@ def gated_scan(zq: torch.Tensor, zf: torch.Tensor, v: torch.Tensor, f_bias: torc
     return o
 
 
+@_timed
 def head_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """fp32 ``[..., dv]`` rows -> ``x * rsqrt(mean(x^2) + eps) * weight`` in the weight's dtype."""
     _need_cuda(x, weight)
@@ -149,6 +177,7 @@ def head_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Ten
     return out
 
 
+@_timed
 def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
     _need_cuda(z, coef)
     out = torch.empty(z.shape, dtype=z.dtype, device=z.device)
@@ -158,6 +187,7 @@ def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
     return out
 
 
+@_timed
 def sigmoid_topk(logits: torch.Tensor, top: int):
     """fp32 ``[n, E]`` logits -> ``(ids int32 [n, top], weights fp32 [n, top])``; weights are sigmoid(logit)."""
     _need_cuda(logits)
@@ -171,6 +201,7 @@ def sigmoid_topk(logits: torch.Tensor, top: int):
     return ids, w
 
 
+@_timed
 def scaled_gather(h: torch.Tensor, weights: torch.Tensor, src: torch.Tensor, top: int) -> torch.Tensor:
     _need_cuda(h, weights, src)
     if not h.is_contiguous() or src.dtype != torch.int64 or weights.dtype != torch.float32:
@@ -182,6 +213,7 @@ def scaled_gather(h: torch.Tensor, weights: torch.Tensor, src: torch.Tensor, top
     return xs
 
 
+@_timed
 def clamped_glu(gu: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
     _need_cuda(gu)
     if not gu.is_contiguous() or gu.shape[1] % 2:
@@ -194,6 +226,7 @@ def clamped_glu(gu: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
     return y
 
 
+@_timed
 def expert_combine(ys: torch.Tensor, where: torch.Tensor, n_tok: int, top: int) -> torch.Tensor:
     _need_cuda(ys, where)
     if not ys.is_contiguous() or where.dtype != torch.int64 or where.numel() != n_tok * top:
