@@ -358,6 +358,246 @@ biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q
   }
 }
 
+// ---- biased attention for prompt portions on the tensor cores (16-bit storage types) --------------------------------
+// A CTA serves up to 64 consecutive tokens of one sequence and ONE query head; warp w owns rows 16 w .. 16 w + 15.
+// Keys are walked in tiles of 64 from position 0.  K and V tiles arrive by cp.async, double buffered, and stay in
+// their storage type; S = Q K^T and O += P V are mma.sync m16n8k16 with fp32 accumulators in registers, the softmax
+// (scale, temperature, bias, causal mask, running max and sum) runs in fp32 on the S fragments, and only the
+// weights P are rounded to the storage type as the left operand of P V.  V fragments come from ldmatrix.trans.
+template <typename T>
+struct Mma16;
+template <>
+struct Mma16<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+};
+template <>
+struct Mma16<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+};
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  const int bytes = valid ? 16 : 0;  // fewer source bytes than 16: the rest is zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kMmaRows = 64;   // query rows per CTA
+constexpr int kMmaKeys = 64;   // keys per tile
+
+template <typename T, int DV8>
+__global__ void __launch_bounds__(128)
+biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stride, const T* __restrict__ gate,
+                              int64_t gate_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                              const int32_t* __restrict__ block_tables, int table_stride,
+                              const AttnTile* __restrict__ tiles, const int32_t* __restrict__ tok_pos,
+                              const float* __restrict__ bias_lut, int lut_len, int lut_in_smem, int q_vec, float scale,
+                              float temp_coef, int temp_every, int H, int G, int dk, int dv, int block_size) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  constexpr int dvp = DV8 * 8;
+  const int ldq = dk + 8, ldv = dvp + 8;       // element strides: 16-byte multiples, conflict-free fragment reads
+  T* q_s = reinterpret_cast<T*>(smem_raw);     // [64][ldq]
+  T* k_s = q_s + kMmaRows * ldq;               // 2 x [64][ldq]
+  T* v_s = k_s + 2 * kMmaKeys * ldq;           // 2 x [64][ldv]
+  float* lut_s = reinterpret_cast<float*>(v_s + 2 * kMmaKeys * ldv);
+  const AttnTile tile = tiles[blockIdx.x];
+  const int h = blockIdx.y, g = h / (H / G);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int pos0 = tok_pos[tile.tok0];
+  const int pos_last = pos0 + tile.count - 1;
+  const int32_t* table = block_tables + static_cast<int64_t>(tile.seq) * table_stride;
+  const float* lut = bias_lut + static_cast<int64_t>(h) * lut_len;
+  if (lut_in_smem) {
+    for (int i = threadIdx.x; i < lut_len; i += blockDim.x) lut_s[i] = lut[i];
+    lut = lut_s;
+  }
+  const int qc = dk / 8, vc = dvp / 8;          // 16-byte chunks per row
+
+  // Q tile (rows beyond the tile's tokens are zero); element-wise when the rows are not 16-byte aligned
+  if (q_vec) {
+    for (int c = threadIdx.x; c < kMmaRows * qc; c += blockDim.x) {
+      const int r = c / qc, e = (c - r * qc) * 8;
+      const bool ok = r < tile.count;
+      cp_async16(q_s + r * ldq + e, ok ? q + (tile.tok0 + r) * q_stride + h * dk + e : q, ok);
+    }
+  } else {
+    for (int i = threadIdx.x; i < kMmaRows * dk; i += blockDim.x) {
+      const int r = i / dk, d = i - r * dk;
+      q_s[r * ldq + d] = r < tile.count ? q[(tile.tok0 + r) * q_stride + h * dk + d] : Cvt<T>::from_f32(0.f);
+    }
+  }
+  auto load_kv = [&](int j0, int stage) {
+    T* kd = k_s + stage * kMmaKeys * ldq;
+    T* vd = v_s + stage * kMmaKeys * ldv;
+    for (int c = threadIdx.x; c < kMmaKeys * qc; c += blockDim.x) {
+      const int j = c / qc, e = (c - j * qc) * 8;
+      const int key = j0 + j;
+      const bool ok = key <= pos_last;
+      const int64_t row = ok ? (static_cast<int64_t>(table[key / block_size]) * G + g) * block_size + key % block_size : 0;
+      cp_async16(kd + j * ldq + e, k_pool + row * dk + e, ok);
+    }
+    for (int c = threadIdx.x; c < kMmaKeys * vc; c += blockDim.x) {
+      const int j = c / vc, e = (c - j * vc) * 8;
+      const int key = j0 + j;
+      const bool ok = key <= pos_last && e < dv;
+      const int64_t row = ok ? (static_cast<int64_t>(table[key / block_size]) * G + g) * block_size + key % block_size : 0;
+      cp_async16(vd + j * ldv + e, v_pool + row * dv + (ok ? e : 0), ok);
+    }
+  };
+  load_kv(0, 0);
+  cp_async_commit();
+
+  const int row_a = warp * 16 + gq;                      // this thread's rows: row_a and row_a + 8
+  int posr[2];
+  float qmul[2], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = row_a + 8 * i;
+    posr[i] = r < tile.count ? pos0 + r : -1;
+    const float steps = static_cast<float>((posr[i] + 1) / max(temp_every, 1));
+    qmul[i] = scale * (1.0f + temp_coef * logf(steps + 1.0f));
+  }
+  const int warp_pos_max = min(pos0 + warp * 16 + 15, pos_last);
+  const bool warp_live = warp * 16 < tile.count;
+  float o[DV8][4];
+#pragma unroll
+  for (int n = 0; n < DV8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+  const int n_kt = pos_last / kMmaKeys + 1;
+  for (int it = 0; it < n_kt; ++it) {
+    if (it + 1 < n_kt) {
+      load_kv((it + 1) * kMmaKeys, (it + 1) & 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const int j0 = it * kMmaKeys;
+    if (warp_live && j0 <= warp_pos_max) {
+      const T* kt = k_s + (it & 1) * kMmaKeys * ldq;
+      const T* vt = v_s + (it & 1) * kMmaKeys * ldv;
+      float s[8][4];
+#pragma unroll
+      for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int kk = 0; kk < dk / 16; ++kk) {
+        uint32_t a[4];
+        const T* qa = q_s + row_a * ldq + kk * 16 + 2 * tq;
+        a[0] = *reinterpret_cast<const uint32_t*>(qa);
+        a[1] = *reinterpret_cast<const uint32_t*>(qa + 8 * ldq);
+        a[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * ldq + 8);
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+          const T* kb = kt + (n * 8 + gq) * ldq + kk * 16 + 2 * tq;
+          Mma16<T>::mma(s[n], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
+        }
+      }
+      // fp32 softmax on the fragments: element e of s[n] is (row gq + 8 (e >> 1), key 8 n + 2 tq + (e & 1))
+      float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = e >> 1;
+          const int key = j0 + n * 8 + 2 * tq + (e & 1);
+          float sc = -INFINITY;
+          if (key <= posr[i]) sc = s[n][e] * qmul[i] + lut[min(posr[i] - key, lut_len - 1)];
+          s[n][e] = sc;
+          mx[i] = fmaxf(mx[i], sc);
+        }
+      }
+      float corr[2], msafe[2];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+        mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+        const float m_new = fmaxf(m[i], mx[i]);
+        msafe[i] = m_new == -INFINITY ? 0.f : m_new;   // a row that sees no key yet keeps weights 0, not NaN
+        corr[i] = expf(m[i] - msafe[i]);
+        m[i] = m_new;
+      }
+      float part[2] = {0.f, 0.f};
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float pexp = expf(s[n][e] - msafe[e >> 1]);
+          s[n][e] = pexp;
+          part[e >> 1] += pexp;
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) l[i] = l[i] * corr[i] + part[i];   // per-thread share of the row sum
+#pragma unroll
+      for (int n = 0; n < DV8; ++n) {
+        o[n][0] *= corr[0];
+        o[n][1] *= corr[0];
+        o[n][2] *= corr[1];
+        o[n][3] *= corr[1];
+      }
+#pragma unroll
+      for (int k2 = 0; k2 < kMmaKeys / 16; ++k2) {
+        uint32_t a[4];
+        a[0] = Mma16<T>::pack(s[2 * k2][0], s[2 * k2][1]);
+        a[1] = Mma16<T>::pack(s[2 * k2][2], s[2 * k2][3]);
+        a[2] = Mma16<T>::pack(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
+        a[3] = Mma16<T>::pack(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+#pragma unroll
+        for (int n = 0; n < DV8; n += 2) {
+          const T* vrow = vt + (k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + n * 8 + (lane >> 4) * 8;
+          const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(vrow));
+          uint32_t b0, b1, b2, b3;
+          asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                       : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3)
+                       : "r"(addr));
+          Mma16<T>::mma(o[n], a, b0, b1);
+          Mma16<T>::mma(o[n + 1], a, b2, b3);
+        }
+      }
+    }
+    __syncthreads();   // the stage just read is the target of the load after next
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
+    l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+    const int r = row_a + 8 * i;
+    if (r >= tile.count) continue;
+    const int64_t n_tok = tile.tok0 + r;
+    const float gt = gate ? sigmoidf_(Cvt<T>::to_f32(gate[n_tok * gate_stride + h])) : 1.0f;
+    const float inv = gt / l[i];
+    T* orow = out + (n_tok * H + h) * dv;
+#pragma unroll
+    for (int n = 0; n < DV8; ++n) {
+      const int col = n * 8 + 2 * tq;
+      if (col < dv) {   // dv is a multiple of 8: col + 1 < dv as well
+        orow[col] = Cvt<T>::from_f32(o[n][2 * i] * inv);
+        orow[col + 1] = Cvt<T>::from_f32(o[n][2 * i + 1] * inv);
+      }
+    }
+  }
+}
+
 // ---- gated linear recurrence ------------------------------------------------------------------------------------
 // One CTA per (sequence, head).  The state [dk][dv] lives in shared memory for the whole portion; thread (rg, c)
 // owns column c and the rows i = rg, rg + RG, ...  Inputs of token t + 1 are fetched while token t is computed.
@@ -704,6 +944,52 @@ int b200_biased_paged_attn(void* out, const void* q, int64_t q_stride, const voi
 #undef B200_ATTN_CASE
 #undef B200_ATTN_DV
     return check_launch("b200_biased_paged_attn");
+  });
+}
+
+int b200_biased_prompt_attn_supported(int dk, int dv, int dtype) {
+  return (dtype == B200_DTYPE_BF16 || dtype == B200_DTYPE_F16) && dk > 0 && dk % 16 == 0 && dk <= 256 && dv > 0 &&
+         dv % 8 == 0 && dv <= 128;
+}
+
+int b200_biased_prompt_attn(void* out, const void* q, int64_t q_stride, const void* gate, int64_t gate_stride,
+                            const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
+                            const int32_t* tiles, int n_tiles, const int32_t* tok_pos, const float* bias_lut,
+                            int lut_len, float scale, float temp_coef, int temp_every, int H, int G, int dk, int dv,
+                            int block_size, int dtype, void* stream) {
+  if (n_tiles < 0 || H <= 0 || G <= 0 || H % G || block_size <= 0 || lut_len <= 0)
+    return fail(B200_EINVAL, "b200_biased_prompt_attn: bad sizes");
+  if (!b200_biased_prompt_attn_supported(dk, dv, dtype))
+    return fail(B200_ESHAPE, "b200_biased_prompt_attn: needs a 16-bit dtype, dk %% 16 == 0 (<= 256), dv %% 8 == 0 (<= 128)");
+  if (n_tiles == 0) return 0;
+  if (!out || !q || !k_pool || !v_pool || !block_tables || !tiles || !tok_pos || !bias_lut)
+    return fail(B200_EINVAL, "b200_biased_prompt_attn: null pointer");
+  if (!aligned16(k_pool) || !aligned16(v_pool))
+    return fail(B200_ESHAPE, "b200_biased_prompt_attn: pools must be 16-byte aligned");
+  const int q_vec = aligned16(q) && (q_stride * 2) % 16 == 0;
+  const int dv8 = dv <= 32 ? 4 : (dv <= 64 ? 8 : 16);
+  const size_t tiles_bytes = 2u * (static_cast<size_t>(kMmaRows) * (dk + 8) * 3 + 2u * kMmaKeys * (dv8 * 8 + 8));
+  const int lut_in_smem = static_cast<size_t>(lut_len) * 4 + tiles_bytes <= 200 * 1024 && lut_len <= 16384;
+  const size_t smem = tiles_bytes + (lut_in_smem ? static_cast<size_t>(lut_len) * 4 : 0);
+  const dim3 grid(n_tiles, H);
+  return mixer_by_dtype(dtype, "b200_biased_prompt_attn", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    if constexpr (std::is_same_v<T, float>) {
+      return fail(B200_ESHAPE, "b200_biased_prompt_attn: 16-bit dtypes only");
+    } else {
+      auto launch = [&](auto kern) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        kern<<<grid, 128, smem, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<T*>(out), static_cast<const T*>(q), q_stride, static_cast<const T*>(gate), gate_stride,
+            static_cast<const T*>(k_pool), static_cast<const T*>(v_pool), block_tables, table_stride,
+            reinterpret_cast<const AttnTile*>(tiles), tok_pos, bias_lut, lut_len, lut_in_smem, q_vec, scale, temp_coef,
+            temp_every, H, G, dk, dv, block_size);
+      };
+      if (dv8 == 4) launch(biased_prompt_attn_mma_kernel<T, 4>);
+      else if (dv8 == 8) launch(biased_prompt_attn_mma_kernel<T, 8>);
+      else launch(biased_prompt_attn_mma_kernel<T, 16>);
+      return check_launch("b200_biased_prompt_attn");
+    }
   });
 }
 

@@ -111,9 +111,11 @@ def attn_tile_tokens(n_tokens: int, H: int, G: int) -> int:
 @_timed
 def biased_paged_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pool: torch.Tensor, v_pool: torch.Tensor,
                            block_tables: torch.Tensor, tiles: torch.Tensor, max_tile_tokens: int, tok_pos: torch.Tensor,
-                           bias_lut: torch.Tensor, scale: float, temp_coef: float, temp_every: int, H: int) -> torch.Tensor:
+                           bias_lut: torch.Tensor, scale: float, temp_coef: float, temp_every: int, H: int,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of packed rows ``q [n, H*dk]`` over the paged cache with a distance-bias table
-    ``bias_lut [H, L]`` (fp32), a query temperature and a sigmoid gate ``gate [n, H]``; returns ``[n, H*dv]``."""
+    ``bias_lut [H, L]`` (fp32), a query temperature and a sigmoid gate ``gate [n, H]``; returns ``[n, H*dv]``
+    (the tiles' rows of ``out`` when given)."""
     _need_cuda(q, k_pool, v_pool, block_tables, tiles, tok_pos, bias_lut)
     nb, G, bs, dk = k_pool.shape
     dv = v_pool.shape[3]
@@ -126,7 +128,8 @@ def biased_paged_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pool
         raise ValueError("tiles must be contiguous int32 [n_tiles, 3]")
     if bias_lut.dtype != torch.float32 or bias_lut.shape[0] != H or not bias_lut.is_contiguous():
         raise ValueError("bias_lut must be contiguous fp32 [H, L]")
-    out = torch.empty((n, H * dv), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((n, H * dv), dtype=q.dtype, device=q.device)
     rc = _lib_().b200_biased_paged_attn(out.data_ptr(), q.data_ptr(), _rows2(q), _ptr(gate),
                                         _rows2(gate) if gate is not None else 0, k_pool.data_ptr(), v_pool.data_ptr(),
                                         block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(), tiles.shape[0],
@@ -135,6 +138,40 @@ def biased_paged_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pool
                                         DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_biased_paged_attn")
     return out
+
+
+PROMPT_TILE_TOKENS = 64     # tokens of one sequence a CTA of the tensor-core prompt kernel serves
+PROMPT_MIN_TOKENS = 16      # shorter portions (and decoded tokens) go through biased_paged_attention
+
+
+def prompt_attention_supported(dk: int, dv: int, dtype: torch.dtype) -> bool:
+    return bool(_lib_().b200_biased_prompt_attn_supported(int(dk), int(dv), DTYPE_ID[dtype]))
+
+
+@_timed
+def biased_prompt_attention(out: torch.Tensor, q: torch.Tensor, gate: Optional[torch.Tensor], k_pool: torch.Tensor,
+                            v_pool: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, tok_pos: torch.Tensor,
+                            bias_lut: torch.Tensor, scale: float, temp_coef: float, temp_every: int, H: int) -> None:
+    """``biased_paged_attention`` for prompt portions on the tensor cores; writes the tiles' rows of ``out``
+    ``[n, H*dv]`` (16-bit dtypes, see ``prompt_attention_supported``).  ``tiles``: up to 64 tokens each."""
+    _need_cuda(out, q, k_pool, v_pool, block_tables, tiles, tok_pos, bias_lut)
+    nb, G, bs, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    n = q.shape[0]
+    if q.shape[1] != H * dk or tuple(out.shape) != (n, H * dv) or not out.is_contiguous() or out.dtype != q.dtype:
+        raise ValueError("q / out do not match the head layout")
+    if gate is not None and tuple(gate.shape) != (n, H):
+        raise ValueError("gate must be [n, H]")
+    if tiles.dtype != torch.int32 or tiles.dim() != 2 or tiles.shape[1] != 3 or not tiles.is_contiguous():
+        raise ValueError("tiles must be contiguous int32 [n_tiles, 3]")
+    if bias_lut.dtype != torch.float32 or bias_lut.shape[0] != H or not bias_lut.is_contiguous():
+        raise ValueError("bias_lut must be contiguous fp32 [H, L]")
+    rc = _lib_().b200_biased_prompt_attn(out.data_ptr(), q.data_ptr(), _rows2(q), _ptr(gate),
+                                         _rows2(gate) if gate is not None else 0, k_pool.data_ptr(), v_pool.data_ptr(),
+                                         block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(), tiles.shape[0],
+                                         tok_pos.data_ptr(), bias_lut.data_ptr(), bias_lut.shape[1], float(scale),
+                                         float(temp_coef), int(temp_every), H, G, dk, dv, bs, DTYPE_ID[q.dtype], _stream())
+    _lib.check_mixers(rc, "b200_biased_prompt_attn")
 
 
 @_timed

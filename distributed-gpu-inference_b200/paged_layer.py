@@ -191,25 +191,35 @@ class RaggedBatchState:
     pending_norm: Optional[torch.Tensor] = None
     _tiles: Optional[dict] = None
 
-    def tiles_for(self, num_heads: int, num_kv_heads: int):
+    def tiles_for(self, num_heads: int, num_kv_heads: int, below: int = 0):
         """``(tiles int32 [n, 3], tokens per tile at most)`` for an attention layer with this head layout: each
-        sequence's tokens cut into runs that one CTA serves, longest context first."""
+        sequence's tokens cut into runs that one CTA of ``biased_paged_attention`` serves, longest context first.
+        ``below`` > 0 keeps only portions shorter than that (the others go to ``prompt_tiles``)."""
         from . import mixer_ops
 
         cap = mixer_ops.attn_tile_tokens(1 << 20, num_heads, num_kv_heads)
+        return self._plan(("row", cap, below), cap, lambda count: below <= 0 or count < below)
+
+    def prompt_tiles(self, at_least: int, cap: int):
+        """Tiles of up to ``cap`` tokens over the portions of ``at_least`` tokens or more (tensor-core prompt kernel)."""
+        return self._plan(("prompt", cap, at_least), cap, lambda count: count >= at_least)
+
+    def _plan(self, key, cap: int, keep):
         if self._tiles is None:
             self._tiles = {}
-        if cap not in self._tiles:
+        if key not in self._tiles:
             rows, most = [], 1
             for first, count, table_row, past in self.spans:
+                if not keep(count):
+                    continue
                 for lo in range(0, count, cap):
                     n = min(cap, count - lo)
                     most = max(most, n)
                     rows.append((past + lo + n, first + lo, n, table_row))
             rows.sort(key=lambda r: -r[0])
             t = torch.tensor([r[1:] for r in rows], dtype=torch.int32).reshape(-1, 3)
-            self._tiles[cap] = (t.to(self.tok_pos.device, non_blocking=True), most)
-        return self._tiles[cap]
+            self._tiles[key] = (t.to(self.tok_pos.device, non_blocking=True), most)
+        return self._tiles[key]
 
 
 @dataclass

@@ -141,8 +141,11 @@ class BiasedPagedAttention(nn.Module):
         self.v_mix = bool(spec.get("v_mix", False))
         self.is_first_mix = is_first_mix
         self.eps = eps
-        self.w_in = _param(torch.cat([t["q"], t["k"], t["v"], t["g"]], dim=0), device, dtype)
+        w_in = torch.cat([t["q"], t["k"], t["v"], t["g"]], dim=0)
+        pad = -w_in.shape[0] % 8     # zero rows: projection rows stay 16-byte aligned for the kernels' vector loads
+        self.w_in = _param(torch.cat([w_in, w_in.new_zeros(pad, w_in.shape[1])], dim=0), device, dtype)
         self.w_o = _param(t["o"], device, dtype)
+        self.tensor_core_prompt = mixer_ops.prompt_attention_supported(self.dk, self.dv, self.w_in.dtype)
         self.register_buffer("bias_lut", distance_bias_table(t["rel"], float(spec["bias_max"])).to(device), persistent=False)
         self.lam = float(t["vmix"].to(torch.float32)) if "vmix" in t else 0.0
 
@@ -161,10 +164,19 @@ class BiasedPagedAttention(nn.Module):
                     raise RuntimeError("value mixing needs the first mixing layer's values of this step (same shape)")
         mixer_ops.value_prep_append(proj[:, a:b], proj[:, b:c], cache.k_pool, cache.v_pool, st.slot_mapping, self.eps,
                                     v_prev=v_prev, lam=self.lam, v_keep=v_keep)
-        tiles, most = st.tiles_for(H, G)
-        attn = mixer_ops.biased_paged_attention(proj[:, :a], proj[:, c:], cache.k_pool, cache.v_pool, st.block_tables,
-                                                tiles, most, st.tok_pos, self.bias_lut, self.scale, self.temp_coef,
-                                                self.temp_every, H)
+        q, gate = proj[:, :a], proj[:, c:c + H]
+        attn = torch.empty((h.shape[0], H * dv), dtype=h.dtype, device=h.device)
+        split = mixer_ops.PROMPT_MIN_TOKENS if self.tensor_core_prompt else 0
+        if split:   # prompt portions: tensor cores; short portions and decoded tokens: the row kernel below
+            tiles, _ = st.prompt_tiles(split, mixer_ops.PROMPT_TILE_TOKENS)
+            if tiles.shape[0]:
+                mixer_ops.biased_prompt_attention(attn, q, gate, cache.k_pool, cache.v_pool, st.block_tables, tiles,
+                                                  st.tok_pos, self.bias_lut, self.scale, self.temp_coef, self.temp_every, H)
+        tiles, most = st.tiles_for(H, G, below=split)
+        if tiles.shape[0]:
+            mixer_ops.biased_paged_attention(q, gate, cache.k_pool, cache.v_pool, st.block_tables, tiles, most,
+                                             st.tok_pos, self.bias_lut, self.scale, self.temp_coef, self.temp_every, H,
+                                             out=attn)
         return F.linear(attn, self.w_o)
 
 

@@ -460,3 +460,115 @@ def test_checkpoint_folder_round_trip(tmp_path):
     toks = tokens(30, CFG_B["vocab"], 6)
     got = whole(RaggedStepEngine(shards, max_tokens=64), "a", toks)
     close(got, R.forward(CFG_B, tensors, toks), 5e-5)
+
+
+# ---- the tensor-core prompt kernel (16-bit storage, dk % 16 == 0, dv % 8 == 0) -----------------------------------------
+
+def _prompt_tiles(spans, cap=64):
+    rows = []
+    for first, count, table_row in spans:
+        for lo in range(0, count, cap):
+            rows.append([first + lo, min(cap, count - lo), table_row])
+    return torch.tensor(rows, dtype=torch.int32)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("H,G,dk,dv", [(4, 2, 32, 48), (2, 1, 96, 32), (3, 3, 16, 128), (2, 2, 48, 8)])
+def test_prompt_kernel_finds_needles_and_respects_edges(dtype, H, G, dk, dv):
+    """Portions that start anywhere (not at a multiple of the 64-key tile or the 16-token page), needles at tile and
+    page borders and among the first and newest keys, a bias table with large steps, a strong temperature; against
+    the plain fp32 attention of the same 16-bit-rounded q, k, v."""
+    from dgi_b200 import mixer_ops as M
+    from dgi_b200 import petipel_layer as P
+
+    assert M.prompt_attention_supported(dk, dv, dtype)
+    n_ctx, rows, far, every, coef = 333, 12, 40, 8, 1.5
+    k, v, k_pool, v_pool, table = _paged_case(n_ctx, G, dk, dv, seed=11)
+    dirs = torch.nn.functional.normalize(torch.randn(40, dk, generator=torch.Generator().manual_seed(12)), dim=-1)
+    needles = [0, 1, 15, 16, 63, 64, 65, 127, 128, 191, 192, 200, 255, 256, 300, 319, 320, 331, 332]
+    for i, j in enumerate(needles):
+        k[j] = 0.05 * k[j] + 5.0 * dirs[i]
+        k_pool[table[0, j // 16].long(), :, j % 16] = k[j]
+    rel = torch.tensor([((-1.0) ** i) * (0.5 + 0.3 * i) for i in range(rows)])[:, None] * torch.linspace(1.0, -1.0, H)[None]
+    lut = P.distance_bias_table(rel, far)
+    q = torch.randn(n_ctx, H, dk, generator=torch.Generator().manual_seed(13)) * 0.2
+    for r in range(n_ctx):
+        for h in range(H):
+            q[r, h] += 5.0 * dirs[(r * H + h) % len(needles)]
+    gate = torch.randn(n_ctx, H, generator=torch.Generator().manual_seed(14))
+    qd, gd = q.reshape(n_ctx, H * dk).to(dtype), gate.to(dtype)
+    kr, vr = k.to(dtype).float(), v.to(dtype).float()
+    ref = _attention_rows(qd.float().view(n_ctx, H, dk), gd.float(), kr, vr, list(range(n_ctx)), rel, far, 0.3, coef,
+                          every, H, G)
+    for lo, n in ((0, n_ctx), (0, 17), (37, 150), (250, 83), (317, 16)):
+        out = torch.full((n, H * dv), 7.0, dtype=dtype, device=DEV)
+        M.biased_prompt_attention(out, qd[lo:lo + n].to(DEV), gd[lo:lo + n].to(DEV), k_pool.to(DEV, dtype),
+                                  v_pool.to(DEV, dtype), table.to(DEV), _prompt_tiles([(0, n, 0)]).to(DEV),
+                                  torch.arange(lo, lo + n, dtype=torch.int32, device=DEV), lut.to(DEV), 0.3, coef, every, H)
+        close(out.float().cpu(), ref[lo:lo + n], 2.5e-2)
+
+
+def test_prompt_kernel_two_sequences_and_unaligned_rows():
+    """Two sequences in one launch (their tiles must not see each other's pages) with q rows taken as column slices
+    of a wider projection whose row stride is not a multiple of 16 bytes."""
+    from dgi_b200 import mixer_ops as M
+
+    H, G, dk, dv = 2, 1, 32, 16
+    ka, va, kpa, vpa, ta = _paged_case(70, G, dk, dv, seed=21)
+    kb, vb, kpb, vpb, tb = _paged_case(100, G, dk, dv, seed=22)
+    nb = kpa.shape[0]
+    k_pool, v_pool = torch.cat([kpa, kpb]), torch.cat([vpa, vpb])
+    width = max(ta.shape[1], tb.shape[1])
+    table = torch.zeros(2, width, dtype=torch.int32)
+    table[0, :ta.shape[1]], table[1, :tb.shape[1]] = ta[0], tb[0] + nb
+    g = torch.Generator().manual_seed(23)
+    wide = torch.randn(170, H * dk + 5, generator=g).to(torch.bfloat16)     # 69 columns: 138-byte rows
+    q = wide[:, :H * dk]
+    pos = torch.cat([torch.arange(70), torch.arange(100)]).to(torch.int32)
+    lut = torch.zeros(H, 5)
+    out = torch.empty(170, H * dv, dtype=torch.bfloat16, device=DEV)
+    M.biased_prompt_attention(out, wide.to(DEV)[:, :H * dk], None, k_pool.to(DEV, torch.bfloat16),
+                              v_pool.to(DEV, torch.bfloat16), table.to(DEV), _prompt_tiles([(0, 70, 0), (70, 100, 1)]).to(DEV),
+                              pos.to(DEV), lut.to(DEV), 0.2, 0.0, 1, H)
+    big = torch.full((170, H), 30.0)
+    rel = torch.zeros(4, H)
+    qa = q.float().view(170, H, dk)
+    ref = torch.cat([
+        _attention_rows(qa[:70], big[:70], ka.bfloat16().float(), va.bfloat16().float(), list(range(70)), rel, 9, 0.2, 0.0, 1, H, G),
+        _attention_rows(qa[70:], big[70:], kb.bfloat16().float(), vb.bfloat16().float(), list(range(100)), rel, 9, 0.2, 0.0, 1, H, G)])
+    close(out.float().cpu(), ref, 2e-2)
+
+
+CFG_C = {  # head sizes the tensor-core prompt kernel takes
+    "architecture": "Petipel", "width": 64, "vocab": 53, "residual_mult": 0.5, "norm": {"eps": 1e-5},
+    "layers": [
+        with_mlp(attn(4, 2, 32, 24, v_mix=True, q_temp={"coef": 0.5, "every": 16}), DENSE),
+        with_mlp(hgrn(2, 16, 32), moe(4, 2)),
+        with_mlp(attn(4, 2, 32, 24, v_mix=True, bias_max=100), DENSE),
+    ],
+}
+
+
+def test_bfloat16_model_with_tensor_core_prompts():
+    """bf16 serving where long portions take the tensor-core kernel and short ones / decoded tokens the row kernel:
+    whole prompt, portions and token-by-token agree with each other and with the fp32 oracle to 16-bit rounding."""
+    eng, tensors = build(CFG_C, dtype=torch.bfloat16)
+    assert eng.shards[0].layers[0].mixer.tensor_core_prompt
+    toks = tokens(150, CFG_C["vocab"], 8)
+    ref = R.forward(CFG_C, tensors, toks)
+    scale = ref.pow(2).mean().sqrt()
+
+    def rel(a, b):
+        d = a - b
+        return ((d - d.mean(1, keepdim=True)).pow(2).mean().sqrt() / scale).item()
+
+    got = whole(eng, "a", toks)
+    assert rel(got, ref) < 0.05
+    at, outs = 0, []
+    for n in (70, 3, 40, 1, 1, 20, 15):
+        outs.append(eng.step([("b", toks[at:at + n], list(range(n)))]))
+        at += n
+    eng.finish("b")
+    assert at == 150 and rel(torch.cat(outs).cpu(), ref) < 0.05 and rel(torch.cat(outs).cpu(), got) < 0.04
+    eng32, _ = build(CFG_C, dtype=torch.float32)
+    close(whole(eng32, "c", toks), ref, 5e-5)
