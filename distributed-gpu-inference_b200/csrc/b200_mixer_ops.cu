@@ -701,6 +701,114 @@ gated_scan_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, const T* 
   }
 }
 
+// Column-per-thread form for key sizes up to 128: thread c keeps column c of the state (dk values) in REGISTERS for
+// the whole portion, so a token costs dk fused multiply-adds per thread and no barrier; q and f of a token are
+// broadcast reads from shared memory.  The CTA stages the activated inputs of 16 tokens at a time, double buffered:
+// raw loads of the next 16 tokens are issued before the current 16 are computed and converted afterwards, one barrier
+// per 16 tokens.  A read-out's row sum is four interleaved partial sums over i in a fixed order, whatever the batch
+// or the portion.
+
+template <typename T, int DK, int NT>
+__global__ void __launch_bounds__(NT)
+gated_scan_columns_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, const T* __restrict__ zf,
+                          const T* __restrict__ v, int64_t in_stride, const T* __restrict__ f_bias,
+                          const T* __restrict__ lower, float* __restrict__ state, const ScanSeq* __restrict__ seqs, int H,
+                          int dk, int dv) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int kScanChunk = DK >= 128 ? 8 : 16;         // tokens staged at a time (fewer when the state fills the registers)
+  const ScanSeq sq = seqs[blockIdx.x];
+  const int h = blockIdx.y;
+  const int col = blockIdx.z * NT + threadIdx.x;
+  const bool has_col = col < dv;
+  const int ncol = min(NT, dv - blockIdx.z * NT);
+  const int row_len = 2 * DK + NT;                       // q[DK] | f[DK] | v[NT] per token, zero padded
+  float* buf0 = smem;
+  float* buf1 = smem + kScanChunk * row_len;
+  float* st = state + (static_cast<int64_t>(sq.slot) * H + h) * dk * dv;
+  float S[DK];
+#pragma unroll
+  for (int i = 0; i < DK; ++i) S[i] = (!sq.fresh && has_col && i < dk) ? st[i * dv + col] : 0.f;
+
+  constexpr int kPer = (kScanChunk * (2 * DK + NT) + NT - 1) / NT;   // staged elements per thread and chunk
+  T raw[kPer];
+  auto fetch = [&](int t0) {
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      const int e = threadIdx.x + u * NT;
+      const int tt = e / row_len, i = e - tt * row_len;
+      raw[u] = Cvt<T>::from_f32(0.f);
+      if (tt < kScanChunk && t0 + tt < sq.count) {
+        const int64_t row = static_cast<int64_t>(sq.tok0 + t0 + tt) * in_stride;
+        if (i < DK) {
+          if (i < dk) raw[u] = zq[row + h * dk + i];
+        } else if (i < 2 * DK) {
+          if (i - DK < dk) raw[u] = zf[row + h * dk + i - DK];
+        } else if (i - 2 * DK < ncol) {
+          raw[u] = v[row + h * dv + blockIdx.z * NT + i - 2 * DK];
+        }
+      }
+    }
+  };
+  auto commit = [&](float* dst) {
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      const int e = threadIdx.x + u * NT;
+      const int tt = e / row_len, i = e - tt * row_len;
+      if (tt < kScanChunk) {
+        const float z = Cvt<T>::to_f32(raw[u]);
+        float r = z;
+        if (i < DK) {
+          r = z * sigmoidf_(z);
+        } else if (i < 2 * DK) {
+          const int d = i - DK;
+          r = 0.f;     // padded rows: f = 0 and q = 0, they never reach a read-out
+          if (d < dk) {
+            const float lo = Cvt<T>::to_f32(lower[h * dk + d]);
+            r = lo + (1.0f - lo) * sigmoidf_(z + Cvt<T>::to_f32(f_bias[h * dk + d]));
+          }
+        }
+        dst[e] = r;
+      }
+    }
+  };
+  fetch(0);
+  commit(buf0);
+  __syncthreads();
+  for (int t0 = 0; t0 < sq.count; t0 += kScanChunk) {
+    const float* cur = ((t0 / kScanChunk) & 1) ? buf1 : buf0;
+    float* nxt = ((t0 / kScanChunk) & 1) ? buf0 : buf1;
+    const bool more = t0 + kScanChunk < sq.count;
+    if (more) fetch(t0 + kScanChunk);
+    const int n_here = min(kScanChunk, sq.count - t0);
+    for (int tt = 0; tt < n_here; ++tt) {
+      const float* row = cur + tt * row_len;
+      const float vc = row[2 * DK + threadIdx.x];
+      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;   // four interleaved partial sums: a fixed order, four short chains
+#pragma unroll
+      for (int i = 0; i < DK; i += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(row + i);
+        const float4 f4 = *reinterpret_cast<const float4*>(row + DK + i);
+        S[i] = f4.x * S[i] + (1.0f - f4.x) * vc;
+        o0 = fmaf(S[i], q4.x, o0);
+        S[i + 1] = f4.y * S[i + 1] + (1.0f - f4.y) * vc;
+        o1 = fmaf(S[i + 1], q4.y, o1);
+        S[i + 2] = f4.z * S[i + 2] + (1.0f - f4.z) * vc;
+        o2 = fmaf(S[i + 2], q4.z, o2);
+        S[i + 3] = f4.w * S[i + 3] + (1.0f - f4.w) * vc;
+        o3 = fmaf(S[i + 3], q4.w, o3);
+      }
+      if (has_col) o_raw[(static_cast<int64_t>(sq.tok0 + t0 + tt) * H + h) * dv + col] = (o0 + o1) + (o2 + o3);
+    }
+    if (more) commit(nxt);
+    __syncthreads();
+  }
+  if (has_col) {
+#pragma unroll
+    for (int i = 0; i < DK; ++i)
+      if (i < dk) st[i * dv + col] = S[i];
+  }
+}
+
 // per-head weighted RMS norm of fp32 rows [rows, dv] -> T; one warp per row
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -999,6 +1107,33 @@ int b200_gated_scan(float* o_raw, const void* zq, const void* zf, const void* v,
   if (n_seqs < 0 || H <= 0 || dk <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_gated_scan: bad sizes");
   if (n_seqs == 0) return 0;
   if (!o_raw || !zq || !zf || !v || !f_bias || !lower || !state || !seqs) return fail(B200_EINVAL, "b200_gated_scan: null pointer");
+  if (dk <= 128) {
+    // column-per-thread kernel: 128 columns per CTA (64 when the value size is small), state in registers
+    // 64 columns per CTA when the value size is small or 128-column CTAs would leave SMs idle (columns are independent)
+    const int nt = (dv <= 64 || static_cast<int64_t>(n_seqs) * H * ((dv + 127) / 128) < 2 * kNumSMs) ? 64 : 128;
+    const int dkt = dk <= 16 ? 16 : (dk <= 32 ? 32 : (dk <= 64 ? 64 : 128));
+    const size_t smem_c = sizeof(float) * 2 * (dkt >= 128 ? 8 : 16) * (2 * static_cast<size_t>(dkt) + nt);
+    const dim3 grid_c(n_seqs, H, (dv + nt - 1) / nt);
+    return mixer_by_dtype(dtype, "b200_gated_scan", [&](auto* tag) {
+      using T = std::remove_pointer_t<decltype(tag)>;
+      auto launch = [&](auto kern) {
+        if (smem_c > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_c));
+        kern<<<grid_c, nt, smem_c, static_cast<cudaStream_t>(stream)>>>(
+            o_raw, static_cast<const T*>(zq), static_cast<const T*>(zf), static_cast<const T*>(v), in_stride,
+            static_cast<const T*>(f_bias), static_cast<const T*>(lower), state, reinterpret_cast<const ScanSeq*>(seqs), H,
+            dk, dv);
+      };
+#define B200_SCAN_CASE(DK_)                                              \
+  if (nt == 64) launch(gated_scan_columns_kernel<T, DK_, 64>);            \
+  else launch(gated_scan_columns_kernel<T, DK_, 128>);
+      if (dkt == 16) { B200_SCAN_CASE(16) }
+      else if (dkt == 32) { B200_SCAN_CASE(32) }
+      else if (dkt == 64) { B200_SCAN_CASE(64) }
+      else { B200_SCAN_CASE(128) }
+#undef B200_SCAN_CASE
+      return check_launch("b200_gated_scan");
+    });
+  }
   if (2 * dk + kScanCols > kScanPF * 256) return fail(B200_ESHAPE, "b200_gated_scan: key size %d beyond %d", dk, (kScanPF * 256 - kScanCols) / 2);
   const size_t smem = sizeof(float) * (static_cast<size_t>(dk) * kScanCols + 2 * (2 * static_cast<size_t>(dk) + kScanCols) +
                                        static_cast<size_t>(kScanRG) * kScanCols);

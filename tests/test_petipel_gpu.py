@@ -266,7 +266,7 @@ def test_value_prep_norms_mixes_and_appends():
         assert torch.equal(k_pool[s // bs, :, s % bs].cpu(), proj[i, :G * dk].view(G, dk))
 
 
-@pytest.mark.parametrize("H,dk,dv", [(3, 10, 24), (1, 8, 70), (2, 33, 300)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 10, 24), (1, 8, 70), (2, 33, 300), (1, 100, 16), (2, 130, 20), (2, 64, 128)])
 def test_gated_recurrence_against_the_loop(H, dk, dv):
     """Portions of unequal sequences in one launch, state carried through the slot pool, stale slots ignored when a
     sequence starts."""
