@@ -168,7 +168,7 @@ biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q
                          float scale, float temp_coef, int temp_every, int H, int G, int dk, int dv, int block_size) {
   // NCH > 0: K / V rows are fetched as 16-byte chunks, NCH per thread, into registers one key tile AHEAD of the
   // tile being computed (needs dk and dv to be multiples of 16 bytes).  NCH == 0: element-wise loads, any sizes.
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int dkp = (dk + 3) & ~3;            // padded row length of K / q rows (multiple of 4 floats)
   const int ks = dkp + 4;                   // K row stride: 16-byte aligned and conflict-free for 128-bit reads
   const int rep = H / G;
@@ -213,43 +213,45 @@ biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q
   const int kc = dk / VN, vc = dv / VN;               // chunks per K / V row
   const int n_chunks = kKeyTile * (kc + vc);
   int4 regs[NR];
-  auto chunk_of = [&](int c, bool& isv, int& j, int& e) {
-    isv = c >= kKeyTile * kc;
-    const int cc = isv ? c - kKeyTile * kc : c;
-    const int per = isv ? vc : kc;
-    j = cc / per;
-    e = (cc - j * per) * VN;
-  };
+  const int bs_shift = (block_size & (block_size - 1)) == 0 ? __ffs(block_size) - 1 : -1;
+  // the chunks a thread moves are the same for every key tile: (is V, key within the tile, first element) once
+  int ch_j[NR], ch_e[NR];
+  bool ch_v[NR], ch_ok[NR];
+#pragma unroll
+  for (int u = 0; u < NR; ++u) {
+    const int c = threadIdx.x + u * kAttnWarps * 32;
+    ch_ok[u] = NCH > 0 && c < n_chunks;
+    ch_v[u] = c >= kKeyTile * kc;
+    const int cc = ch_v[u] ? c - kKeyTile * kc : c;
+    const int per = max(ch_v[u] ? vc : kc, 1);
+    ch_j[u] = cc / per;
+    ch_e[u] = (cc - ch_j[u] * per) * VN;
+  }
   auto prefetch = [&](int j0) {
     const int n_keys = min(kKeyTile, pos_last + 1 - j0);
 #pragma unroll
     for (int u = 0; u < NR; ++u) {
-      const int c = threadIdx.x + u * kAttnWarps * 32;
       regs[u] = make_int4(0, 0, 0, 0);
-      if (c < n_chunks) {
-        bool isv;
-        int j, e;
-        chunk_of(c, isv, j, e);
-        if (j < n_keys) {
-          const int key = j0 + j;
-          const int64_t row = (static_cast<int64_t>(table[key / block_size]) * G + g) * block_size + key % block_size;
-          regs[u] = *reinterpret_cast<const int4*>(isv ? v_pool + row * dv + e : k_pool + row * dk + e);
-        }
+      if (ch_ok[u] && ch_j[u] < n_keys) {
+        const int key = j0 + ch_j[u];
+        const int bi = bs_shift >= 0 ? key >> bs_shift : key / block_size;   // pages are a power of two as a rule
+        const int64_t row = (static_cast<int64_t>(table[bi]) * G + g) * block_size + (key - bi * block_size);
+        regs[u] = *reinterpret_cast<const int4*>(ch_v[u] ? v_pool + row * dv + ch_e[u] : k_pool + row * dk + ch_e[u]);
       }
     }
   };
   auto commit = [&]() {
 #pragma unroll
     for (int u = 0; u < NR; ++u) {
-      const int c = threadIdx.x + u * kAttnWarps * 32;
-      if (c < n_chunks) {
-        bool isv;
-        int j, e;
-        chunk_of(c, isv, j, e);
+      if (ch_ok[u]) {
         const T* el = reinterpret_cast<const T*>(&regs[u]);
-        float* dst = isv ? v_s + j * dv + e : k_s + j * ks + e;
-#pragma unroll
-        for (int i = 0; i < VN; ++i) dst[i] = Cvt<T>::to_f32(el[i]);
+        float* dst = ch_v[u] ? v_s + ch_j[u] * dv + ch_e[u] : k_s + ch_j[u] * ks + ch_e[u];
+        if constexpr (VN == 8) {
+          *reinterpret_cast<float4*>(dst) = make_float4(Cvt<T>::to_f32(el[0]), Cvt<T>::to_f32(el[1]), Cvt<T>::to_f32(el[2]), Cvt<T>::to_f32(el[3]));
+          *reinterpret_cast<float4*>(dst + 4) = make_float4(Cvt<T>::to_f32(el[4]), Cvt<T>::to_f32(el[5]), Cvt<T>::to_f32(el[6]), Cvt<T>::to_f32(el[7]));
+        } else {
+          *reinterpret_cast<float4*>(dst) = make_float4(Cvt<T>::to_f32(el[0]), Cvt<T>::to_f32(el[1]), Cvt<T>::to_f32(el[2]), Cvt<T>::to_f32(el[3]));
+        }
       }
     }
   };
@@ -287,6 +289,7 @@ biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q
       if (j0 + kKeyTile <= pos_last) prefetch(j0 + kKeyTile);
     }
 
+    if (warp * RW < n_rows) {   // warps without a live row only help with the loads and barriers
     // scores: lane = key of the tile
     float s[RW];
 #pragma unroll
@@ -339,6 +342,7 @@ biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q
 #pragma unroll
         for (int c = 0; c < DVL; ++c) acc[r][c] = fmaf(pj, vv[c], acc[r][c]);
       }
+    }
     }
   }
 
@@ -445,22 +449,31 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
       q_s[r * ldq + d] = r < tile.count ? q[(tile.tok0 + r) * q_stride + h * dk + d] : Cvt<T>::from_f32(0.f);
     }
   }
+  // a thread always moves the same 16-byte column of the rows j = row0, row0 + step, ...: no division per chunk
+  const int bs_shift = (block_size & (block_size - 1)) == 0 ? __ffs(block_size) - 1 : -1;
+  const int k_step = blockDim.x / qc, k_row0 = threadIdx.x / qc, k_e = (threadIdx.x - k_row0 * qc) * 8;
+  const int v_step = blockDim.x / vc, v_row0 = threadIdx.x / vc, v_e = (threadIdx.x - v_row0 * vc) * 8;
+  auto pool_row = [&](int key) -> int64_t {
+    const int bi = bs_shift >= 0 ? key >> bs_shift : key / block_size;
+    return (static_cast<int64_t>(table[bi]) * G + g) * block_size + (key - bi * block_size);
+  };
   auto load_kv = [&](int j0, int stage) {
     T* kd = k_s + stage * kMmaKeys * ldq;
     T* vd = v_s + stage * kMmaKeys * ldv;
-    for (int c = threadIdx.x; c < kMmaKeys * qc; c += blockDim.x) {
-      const int j = c / qc, e = (c - j * qc) * 8;
-      const int key = j0 + j;
-      const bool ok = key <= pos_last;
-      const int64_t row = ok ? (static_cast<int64_t>(table[key / block_size]) * G + g) * block_size + key % block_size : 0;
-      cp_async16(kd + j * ldq + e, k_pool + row * dk + e, ok);
+    if (k_row0 < k_step) {
+      for (int j = k_row0; j < kMmaKeys; j += k_step) {
+        const int key = j0 + j;
+        const bool ok = key <= pos_last;
+        cp_async16(kd + j * ldq + k_e, k_pool + (ok ? pool_row(key) * dk + k_e : 0), ok);
+      }
     }
-    for (int c = threadIdx.x; c < kMmaKeys * vc; c += blockDim.x) {
-      const int j = c / vc, e = (c - j * vc) * 8;
-      const int key = j0 + j;
-      const bool ok = key <= pos_last && e < dv;
-      const int64_t row = ok ? (static_cast<int64_t>(table[key / block_size]) * G + g) * block_size + key % block_size : 0;
-      cp_async16(vd + j * ldv + e, v_pool + row * dv + (ok ? e : 0), ok);
+    if (v_row0 < v_step) {
+      const bool col_ok = v_e < dv;
+      for (int j = v_row0; j < kMmaKeys; j += v_step) {
+        const int key = j0 + j;
+        const bool ok = col_ok && key <= pos_last;
+        cp_async16(vd + j * ldv + v_e, v_pool + (ok ? pool_row(key) * dv + v_e : 0), ok);
+      }
     }
   };
   load_kv(0, 0);
@@ -701,50 +714,60 @@ gated_scan_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, const T* 
   }
 }
 
-// Column-per-thread form for key sizes up to 128: thread c keeps column c of the state (dk values) in REGISTERS for
-// the whole portion, so a token costs dk fused multiply-adds per thread and no barrier; q and f of a token are
-// broadcast reads from shared memory.  The CTA stages the activated inputs of 16 tokens at a time, double buffered:
-// raw loads of the next 16 tokens are issued before the current 16 are computed and converted afterwards, one barrier
-// per 16 tokens.  A read-out's row sum is four interleaved partial sums over i in a fixed order, whatever the batch
-// or the portion.
+// Register form for key sizes up to 128: four adjacent lanes share a value column, lane r of the four keeps the state
+// rows i = r, r + 4, ... of that column in REGISTERS for the whole portion.  A token costs dk / 4 state updates per
+// thread, two shuffles to add the four partial read-outs, and no barrier; q and f of a token are broadcast reads
+// from shared memory, stored there grouped by r.  The CTA (128 threads = 32 columns) stages the activated inputs of
+// 16 tokens at a time, double buffered: raw loads of the next 16 tokens are issued before the current 16 are
+// computed and converted afterwards, one barrier per 16 tokens.  The summation order of a read-out is fixed by dk.
+constexpr int kScanChunk = 16;
+constexpr int kScanNT = 128;
+constexpr int kScanColsR = kScanNT / 4;   // value columns per CTA
 
-template <typename T, int DK, int NT>
-__global__ void __launch_bounds__(NT)
+template <typename T, int DK>
+__global__ void __launch_bounds__(kScanNT)
 gated_scan_columns_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, const T* __restrict__ zf,
                           const T* __restrict__ v, int64_t in_stride, const T* __restrict__ f_bias,
                           const T* __restrict__ lower, float* __restrict__ state, const ScanSeq* __restrict__ seqs, int H,
                           int dk, int dv) {
   extern __shared__ __align__(16) float smem[];
-  constexpr int kScanChunk = DK >= 128 ? 8 : 16;         // tokens staged at a time (fewer when the state fills the registers)
+  constexpr int RW4 = DK / 4;                           // state rows per thread
   const ScanSeq sq = seqs[blockIdx.x];
   const int h = blockIdx.y;
-  const int col = blockIdx.z * NT + threadIdx.x;
+  const int r = threadIdx.x & 3;
+  const int cl = threadIdx.x >> 2;                       // column within the CTA
+  const int col0 = blockIdx.z * kScanColsR;
+  const int col = col0 + cl;
   const bool has_col = col < dv;
-  const int ncol = min(NT, dv - blockIdx.z * NT);
-  const int row_len = 2 * DK + NT;                       // q[DK] | f[DK] | v[NT] per token, zero padded
+  const int ncol = min(kScanColsR, dv - col0);
+  constexpr int row_len = 2 * DK + kScanColsR;           // q grouped by r [4][RW4] | f likewise | v[32]
   float* buf0 = smem;
   float* buf1 = smem + kScanChunk * row_len;
   float* st = state + (static_cast<int64_t>(sq.slot) * H + h) * dk * dv;
-  float S[DK];
+  float S[RW4];
 #pragma unroll
-  for (int i = 0; i < DK; ++i) S[i] = (!sq.fresh && has_col && i < dk) ? st[i * dv + col] : 0.f;
-
-  constexpr int kPer = (kScanChunk * (2 * DK + NT) + NT - 1) / NT;   // staged elements per thread and chunk
+  for (int k = 0; k < RW4; ++k) {
+    const int i = 4 * k + r;
+    S[k] = (!sq.fresh && has_col && i < dk) ? st[i * dv + col] : 0.f;
+  }
+  constexpr int kPer = (kScanChunk * row_len + kScanNT - 1) / kScanNT;   // staged elements per thread and chunk
   T raw[kPer];
+  // staged element e of a chunk: token e / row_len, slot s = e % row_len; slots [0, DK) hold q with slot = r * RW4 + k
+  // for row i = 4 k + r, slots [DK, 2 DK) hold f the same way, the rest the CTA's value columns
   auto fetch = [&](int t0) {
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {
-      const int e = threadIdx.x + u * NT;
-      const int tt = e / row_len, i = e - tt * row_len;
+      const int e = threadIdx.x + u * kScanNT;
+      const int tt = e / row_len, sl = e - tt * row_len;
       raw[u] = Cvt<T>::from_f32(0.f);
       if (tt < kScanChunk && t0 + tt < sq.count) {
         const int64_t row = static_cast<int64_t>(sq.tok0 + t0 + tt) * in_stride;
-        if (i < DK) {
-          if (i < dk) raw[u] = zq[row + h * dk + i];
-        } else if (i < 2 * DK) {
-          if (i - DK < dk) raw[u] = zf[row + h * dk + i - DK];
-        } else if (i - 2 * DK < ncol) {
-          raw[u] = v[row + h * dv + blockIdx.z * NT + i - 2 * DK];
+        if (sl < 2 * DK) {
+          const int s2 = sl < DK ? sl : sl - DK;
+          const int i = 4 * (s2 % RW4) + s2 / RW4;
+          if (i < dk) raw[u] = sl < DK ? zq[row + h * dk + i] : zf[row + h * dk + i];
+        } else if (sl - 2 * DK < ncol) {
+          raw[u] = v[row + h * dv + col0 + sl - 2 * DK];
         }
       }
     }
@@ -752,22 +775,23 @@ gated_scan_columns_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, c
   auto commit = [&](float* dst) {
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {
-      const int e = threadIdx.x + u * NT;
-      const int tt = e / row_len, i = e - tt * row_len;
+      const int e = threadIdx.x + u * kScanNT;
+      const int tt = e / row_len, sl = e - tt * row_len;
       if (tt < kScanChunk) {
         const float z = Cvt<T>::to_f32(raw[u]);
-        float r = z;
-        if (i < DK) {
-          r = z * sigmoidf_(z);
-        } else if (i < 2 * DK) {
-          const int d = i - DK;
-          r = 0.f;     // padded rows: f = 0 and q = 0, they never reach a read-out
-          if (d < dk) {
-            const float lo = Cvt<T>::to_f32(lower[h * dk + d]);
-            r = lo + (1.0f - lo) * sigmoidf_(z + Cvt<T>::to_f32(f_bias[h * dk + d]));
+        float val = z;
+        if (sl < DK) {
+          val = z * sigmoidf_(z);
+        } else if (sl < 2 * DK) {
+          const int s2 = sl - DK;
+          const int i = 4 * (s2 % RW4) + s2 / RW4;
+          val = 0.f;   // padded rows: f = 0 and q = 0, they never reach a read-out
+          if (i < dk) {
+            const float lo = Cvt<T>::to_f32(lower[h * dk + i]);
+            val = lo + (1.0f - lo) * sigmoidf_(z + Cvt<T>::to_f32(f_bias[h * dk + i]));
           }
         }
-        dst[e] = r;
+        dst[e] = val;
       }
     }
   };
@@ -782,30 +806,37 @@ gated_scan_columns_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, c
     const int n_here = min(kScanChunk, sq.count - t0);
     for (int tt = 0; tt < n_here; ++tt) {
       const float* row = cur + tt * row_len;
-      const float vc = row[2 * DK + threadIdx.x];
-      float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;   // four interleaved partial sums: a fixed order, four short chains
+      const float vc = row[2 * DK + cl];
+      const float* qr = row + r * RW4;
+      const float* fr = row + DK + r * RW4;
+      float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < DK; i += 4) {
-        const float4 q4 = *reinterpret_cast<const float4*>(row + i);
-        const float4 f4 = *reinterpret_cast<const float4*>(row + DK + i);
-        S[i] = f4.x * S[i] + (1.0f - f4.x) * vc;
-        o0 = fmaf(S[i], q4.x, o0);
-        S[i + 1] = f4.y * S[i + 1] + (1.0f - f4.y) * vc;
-        o1 = fmaf(S[i + 1], q4.y, o1);
-        S[i + 2] = f4.z * S[i + 2] + (1.0f - f4.z) * vc;
-        o2 = fmaf(S[i + 2], q4.z, o2);
-        S[i + 3] = f4.w * S[i + 3] + (1.0f - f4.w) * vc;
-        o3 = fmaf(S[i + 3], q4.w, o3);
+      for (int k = 0; k < RW4; k += 4) {
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + k);
+        const float4 f4 = *reinterpret_cast<const float4*>(fr + k);
+        S[k] = f4.x * S[k] + (1.0f - f4.x) * vc;
+        o0 = fmaf(S[k], q4.x, o0);
+        S[k + 1] = f4.y * S[k + 1] + (1.0f - f4.y) * vc;
+        o1 = fmaf(S[k + 1], q4.y, o1);
+        S[k + 2] = f4.z * S[k + 2] + (1.0f - f4.z) * vc;
+        o0 = fmaf(S[k + 2], q4.z, o0);
+        S[k + 3] = f4.w * S[k + 3] + (1.0f - f4.w) * vc;
+        o1 = fmaf(S[k + 3], q4.w, o1);
       }
-      if (has_col) o_raw[(static_cast<int64_t>(sq.tok0 + t0 + tt) * H + h) * dv + col] = (o0 + o1) + (o2 + o3);
+      float o = o0 + o1;
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (r == 0 && has_col) o_raw[(static_cast<int64_t>(sq.tok0 + t0 + tt) * H + h) * dv + col] = o;
     }
     if (more) commit(nxt);
     __syncthreads();
   }
   if (has_col) {
 #pragma unroll
-    for (int i = 0; i < DK; ++i)
-      if (i < dk) st[i * dv + col] = S[i];
+    for (int k = 0; k < RW4; ++k) {
+      const int i = 4 * k + r;
+      if (i < dk) st[i * dv + col] = S[k];
+    }
   }
 }
 
@@ -1108,29 +1139,22 @@ int b200_gated_scan(float* o_raw, const void* zq, const void* zf, const void* v,
   if (n_seqs == 0) return 0;
   if (!o_raw || !zq || !zf || !v || !f_bias || !lower || !state || !seqs) return fail(B200_EINVAL, "b200_gated_scan: null pointer");
   if (dk <= 128) {
-    // column-per-thread kernel: 128 columns per CTA (64 when the value size is small), state in registers
-    // 64 columns per CTA when the value size is small or 128-column CTAs would leave SMs idle (columns are independent)
-    const int nt = (dv <= 64 || static_cast<int64_t>(n_seqs) * H * ((dv + 127) / 128) < 2 * kNumSMs) ? 64 : 128;
+    // register kernel: 32 value columns per CTA, four lanes per column
     const int dkt = dk <= 16 ? 16 : (dk <= 32 ? 32 : (dk <= 64 ? 64 : 128));
-    const size_t smem_c = sizeof(float) * 2 * (dkt >= 128 ? 8 : 16) * (2 * static_cast<size_t>(dkt) + nt);
-    const dim3 grid_c(n_seqs, H, (dv + nt - 1) / nt);
+    const size_t smem_c = sizeof(float) * 2 * kScanChunk * (2 * static_cast<size_t>(dkt) + kScanColsR);
+    const dim3 grid_c(n_seqs, H, (dv + kScanColsR - 1) / kScanColsR);
     return mixer_by_dtype(dtype, "b200_gated_scan", [&](auto* tag) {
       using T = std::remove_pointer_t<decltype(tag)>;
       auto launch = [&](auto kern) {
-        if (smem_c > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_c));
-        kern<<<grid_c, nt, smem_c, static_cast<cudaStream_t>(stream)>>>(
+        kern<<<grid_c, kScanNT, smem_c, static_cast<cudaStream_t>(stream)>>>(
             o_raw, static_cast<const T*>(zq), static_cast<const T*>(zf), static_cast<const T*>(v), in_stride,
             static_cast<const T*>(f_bias), static_cast<const T*>(lower), state, reinterpret_cast<const ScanSeq*>(seqs), H,
             dk, dv);
       };
-#define B200_SCAN_CASE(DK_)                                              \
-  if (nt == 64) launch(gated_scan_columns_kernel<T, DK_, 64>);            \
-  else launch(gated_scan_columns_kernel<T, DK_, 128>);
-      if (dkt == 16) { B200_SCAN_CASE(16) }
-      else if (dkt == 32) { B200_SCAN_CASE(32) }
-      else if (dkt == 64) { B200_SCAN_CASE(64) }
-      else { B200_SCAN_CASE(128) }
-#undef B200_SCAN_CASE
+      if (dkt == 16) launch(gated_scan_columns_kernel<T, 16>);
+      else if (dkt == 32) launch(gated_scan_columns_kernel<T, 32>);
+      else if (dkt == 64) launch(gated_scan_columns_kernel<T, 64>);
+      else launch(gated_scan_columns_kernel<T, 128>);
       return check_launch("b200_gated_scan");
     });
   }
