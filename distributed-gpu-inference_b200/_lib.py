@@ -117,7 +117,7 @@ MIXER_SIGNATURES = {
                 c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_gated_scan": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                c_int, c_int, c_int, c_void_p]),
+                c_int, c_int, c_int, c_int, c_void_p]),
     "b200_head_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_float, c_int64, c_int, c_int, c_void_p]),
     "b200_polynorm": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_float, c_int, c_int, c_int, c_void_p]),
     "b200_sigmoid_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

@@ -745,11 +745,21 @@ gated_scan_columns_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, c
   float* buf1 = smem + kScanChunk * row_len;
   float* st = state + (static_cast<int64_t>(sq.slot) * H + h) * dk * dv;
   float S[RW4];
+  // the CTA's slab of the state ([dk][32 columns]) moves through shared memory so that global rows are read and
+  // written as whole 128-byte segments; the staging buffers are free at both ends of the kernel
+  if (!sq.fresh) {
+    for (int idx = threadIdx.x; idx < dk * kScanColsR; idx += kScanNT) {
+      const int i = idx / kScanColsR, c = idx - i * kScanColsR;
+      smem[idx] = c < ncol ? st[i * dv + col0 + c] : 0.f;
+    }
+    __syncthreads();
+  }
 #pragma unroll
   for (int k = 0; k < RW4; ++k) {
     const int i = 4 * k + r;
-    S[k] = (!sq.fresh && has_col && i < dk) ? st[i * dv + col] : 0.f;
+    S[k] = (!sq.fresh && i < dk) ? smem[i * kScanColsR + cl] : 0.f;
   }
+  __syncthreads();
   constexpr int kPer = (kScanChunk * row_len + kScanNT - 1) / kScanNT;   // staged elements per thread and chunk
   T raw[kPer];
   // staged element e of a chunk: token e / row_len, slot s = e % row_len; slots [0, DK) hold q with slot = r * RW4 + k
@@ -772,12 +782,12 @@ gated_scan_columns_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, c
       }
     }
   };
-  auto commit = [&](float* dst) {
+  auto commit = [&](float* dst, int n_valid) {   // tokens beyond the portion are not activated (nor read later)
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {
       const int e = threadIdx.x + u * kScanNT;
       const int tt = e / row_len, sl = e - tt * row_len;
-      if (tt < kScanChunk) {
+      if (tt < n_valid) {
         const float z = Cvt<T>::to_f32(raw[u]);
         float val = z;
         if (sl < DK) {
@@ -796,7 +806,7 @@ gated_scan_columns_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, c
     }
   };
   fetch(0);
-  commit(buf0);
+  commit(buf0, min(kScanChunk, sq.count));
   __syncthreads();
   for (int t0 = 0; t0 < sq.count; t0 += kScanChunk) {
     const float* cur = ((t0 / kScanChunk) & 1) ? buf1 : buf0;
@@ -828,15 +838,18 @@ gated_scan_columns_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, c
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       if (r == 0 && has_col) o_raw[(static_cast<int64_t>(sq.tok0 + t0 + tt) * H + h) * dv + col] = o;
     }
-    if (more) commit(nxt);
+    if (more) commit(nxt, min(kScanChunk, sq.count - t0 - kScanChunk));
     __syncthreads();
   }
-  if (has_col) {
 #pragma unroll
-    for (int k = 0; k < RW4; ++k) {
-      const int i = 4 * k + r;
-      if (i < dk) st[i * dv + col] = S[k];
-    }
+  for (int k = 0; k < RW4; ++k) {
+    const int i = 4 * k + r;
+    if (i < dk) smem[i * kScanColsR + cl] = S[k];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < dk * kScanColsR; idx += kScanNT) {
+    const int i = idx / kScanColsR, c = idx - i * kScanColsR;
+    if (c < ncol) st[i * dv + col0 + c] = smem[idx];
   }
 }
 
@@ -1133,12 +1146,12 @@ int b200_biased_prompt_attn(void* out, const void* q, int64_t q_stride, const vo
 }
 
 int b200_gated_scan(float* o_raw, const void* zq, const void* zf, const void* v, int64_t in_stride, const void* f_bias,
-                    const void* lower, float* state, const int32_t* seqs, int n_seqs, int H, int dk, int dv, int dtype,
-                    void* stream) {
+                    const void* lower, float* state, const int32_t* seqs, int n_seqs, int max_count, int H, int dk, int dv,
+                    int dtype, void* stream) {
   if (n_seqs < 0 || H <= 0 || dk <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_gated_scan: bad sizes");
   if (n_seqs == 0) return 0;
   if (!o_raw || !zq || !zf || !v || !f_bias || !lower || !state || !seqs) return fail(B200_EINVAL, "b200_gated_scan: null pointer");
-  if (dk <= 128) {
+  if (dk <= 128 && max_count >= 8) {
     // register kernel: 32 value columns per CTA, four lanes per column
     const int dkt = dk <= 16 ? 16 : (dk <= 32 ? 32 : (dk <= 64 ? 64 : 128));
     const size_t smem_c = sizeof(float) * 2 * kScanChunk * (2 * static_cast<size_t>(dkt) + kScanColsR);

@@ -176,10 +176,11 @@ def biased_prompt_attention(out: torch.Tensor, q: torch.Tensor, gate: Optional[t
 
 @_timed
 def gated_scan(zq: torch.Tensor, zf: torch.Tensor, v: torch.Tensor, f_bias: torch.Tensor, lower: torch.Tensor,
-               state: torch.Tensor, seqs: torch.Tensor, H: int) -> torch.Tensor:
+               state: torch.Tensor, seqs: torch.Tensor, H: int, max_count: int = 1 << 20) -> torch.Tensor:
     """Gated linear recurrence over each sequence's tokens; ``state`` fp32 ``[slots, H, dk, dv]`` is read (unless the
     sequence is fresh) and written back.  ``zq / zf [n, H*dk]``, ``v [n, H*dv]`` are column slices of ONE projection
-    (same row stride).  Returns the raw read-outs, fp32 ``[n, H, dv]``."""
+    (same row stride).  ``max_count``: the largest token count in ``seqs`` (picks the kernel; a hint, not a bound).
+    Returns the raw read-outs, fp32 ``[n, H, dv]``."""
     _need_cuda(zq, zf, v, state, seqs)
     n = zq.shape[0]
     _, Hs, dk, dv = state.shape
@@ -194,7 +195,7 @@ def gated_scan(zq: torch.Tensor, zf: torch.Tensor, v: torch.Tensor, f_bias: torc
         raise ValueError("seqs must be contiguous int32 [n_seqs, 4]")
     o = torch.empty((n, H, dv), dtype=torch.float32, device=zq.device)
     rc = _lib_().b200_gated_scan(o.data_ptr(), zq.data_ptr(), zf.data_ptr(), v.data_ptr(), stride, f_bias.data_ptr(),
-                                 lower.data_ptr(), state.data_ptr(), seqs.data_ptr(), seqs.shape[0], H, dk, dv,
+                                 lower.data_ptr(), state.data_ptr(), seqs.data_ptr(), seqs.shape[0], int(max_count), H, dk, dv,
                                  DTYPE_ID[zq.dtype], _stream())
     _lib.check_mixers(rc, "b200_gated_scan")
     return o

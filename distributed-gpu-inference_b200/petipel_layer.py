@@ -198,7 +198,7 @@ class GatedLinearRecurrence(nn.Module):
         n, a = h.shape[0], self.H * self.dk
         proj = F.linear(h, self.w_in)
         o = mixer_ops.gated_scan(proj[:, :a], proj[:, a:2 * a], proj[:, 2 * a:], self.f_bias, self.lower, cache.rstate,
-                                 cache.state.scan_seqs, self.H)
+                                 cache.state.scan_seqs, self.H, max_count=max(sp[1] for sp in cache.state.spans))
         return F.linear(mixer_ops.head_rmsnorm(o, self.norm_w, self.eps).view(n, self.H * self.dv), self.w_o)
 
 

@@ -71,10 +71,12 @@ int b200_biased_prompt_attn(void* out, const void* q, int64_t q_stride, const vo
 /* Gated linear recurrence per (sequence, head) over the sequence's tokens of this step, in order:
  *   q = silu(zq), f = lower + (1 - lower) * sigmoid(zf + f_bias), S <- diag(f) S + (1 - f) v^T, o = S^T q.
  * state: fp32 [slots, H, dk, dv]; seqs: int32 [n_seqs, 4] = (first packed row, token count, state slot, fresh);
- * fresh != 0 starts from a zero state.  The final state is written back.  o_raw: fp32 [n_tok, H, dv]. */
+ * fresh != 0 starts from a zero state.  The final state is written back.  o_raw: fp32 [n_tok, H, dv].  max_count: the
+ * largest token count among seqs (a hint: portions of 8 tokens or more and key sizes up to 128 take the kernel that
+ * keeps the state in registers, steps of single tokens the one that keeps it in shared memory). */
 int b200_gated_scan(float* o_raw, const void* zq, const void* zf, const void* v, int64_t in_stride, const void* f_bias,
-                    const void* lower, float* state, const int32_t* seqs, int n_seqs, int H, int dk, int dv, int dtype,
-                    void* stream);
+                    const void* lower, float* state, const int32_t* seqs, int n_seqs, int max_count, int H, int dk, int dv,
+                    int dtype, void* stream);
 
 /* out[r] = x[r] * rsqrt(mean(x[r]^2) + eps) * weight;  x fp32 [rows, dv], weight T [dv], out T. */
 int b200_head_rmsnorm(void* out, const float* x, const void* weight, float eps, int64_t rows, int dv, int dtype,

@@ -35,7 +35,7 @@ def test_mixers_library_matches_its_header():
     assert lib.b200_biased_attn_tile_tokens(1, 4, 1) == 1
     rc = lib.b200_polynorm(None, None, 0, None, 1e-6, 4, 8, 7, None)  # dtype 7
     assert rc == -1 and b"null pointer" in lib.b200_mixers_last_error()
-    rc = lib.b200_gated_scan(None, None, None, None, 0, None, None, None, None, 1, 0, 4, 4, 2, None)
+    rc = lib.b200_gated_scan(None, None, None, None, 0, None, None, None, None, 1, 1, 0, 4, 4, 2, None)
     assert rc == -1 and b"bad sizes" in lib.b200_mixers_last_error()
 
 

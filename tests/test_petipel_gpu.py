@@ -267,7 +267,8 @@ def test_value_prep_norms_mixes_and_appends():
 
 
 @pytest.mark.parametrize("H,dk,dv", [(3, 10, 24), (1, 8, 70), (2, 33, 300), (1, 100, 16), (2, 130, 20), (2, 64, 128)])
-def test_gated_recurrence_against_the_loop(H, dk, dv):
+@pytest.mark.parametrize("hint", [1 << 20, 1])      # long portions: state in registers; single tokens: in shared memory
+def test_gated_recurrence_against_the_loop(H, dk, dv, hint):
     """Portions of unequal sequences in one launch, state carried through the slot pool, stale slots ignored when a
     sequence starts."""
     from dgi_b200 import mixer_ops as M
@@ -299,7 +300,7 @@ def test_gated_recurrence_against_the_loop(H, dk, dv):
         proj = torch.nn.functional.linear(h, torch.cat([t["q"], t["f"], t["v"]]).to(DEV))
         a = H * dk
         o = M.gated_scan(proj[:, :a], proj[:, a:2 * a], proj[:, 2 * a:], t["f.b"].to(DEV), t["lower"].to(DEV), state,
-                         torch.tensor(seqs, dtype=torch.int32, device=DEV), H)
+                         torch.tensor(seqs, dtype=torch.int32, device=DEV), H, max_count=hint)
         on = M.head_rmsnorm(o, t["norm"].to(DEV), 1e-5).cpu().view(h.shape[0], H * dv)
         at = 0
         for b, n in owner:
