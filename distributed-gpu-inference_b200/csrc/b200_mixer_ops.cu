@@ -415,6 +415,7 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
                               const AttnTile* __restrict__ tiles, const int32_t* __restrict__ tok_pos,
                               const float* __restrict__ bias_lut, int lut_len, int lut_in_smem, int q_vec, float scale,
                               float temp_coef, int temp_every, int H, int G, int dk, int dv, int block_size) {
+  // Row r of the CTA's 64 is (token r / rep, head g * rep + r % rep): the heads of a kv group share the K / V tiles.
   extern __shared__ __align__(16) unsigned char smem_raw[];
   constexpr int dvp = DV8 * 8;
   const int ldq = dk + 8, ldv = dvp + 8;       // element strides: 16-byte multiples, conflict-free fragment reads
@@ -423,30 +424,31 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
   T* v_s = k_s + 2 * kMmaKeys * ldq;           // 2 x [64][ldv]
   float* lut_s = reinterpret_cast<float*>(v_s + 2 * kMmaKeys * ldv);
   const AttnTile tile = tiles[blockIdx.x];
-  const int h = blockIdx.y, g = h / (H / G);
+  const int g = blockIdx.y, rep = H / G;
+  const int n_rows = tile.count * rep;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gq = lane >> 2, tq = lane & 3;
   const int pos0 = tok_pos[tile.tok0];
   const int pos_last = pos0 + tile.count - 1;
   const int32_t* table = block_tables + static_cast<int64_t>(tile.seq) * table_stride;
-  const float* lut = bias_lut + static_cast<int64_t>(h) * lut_len;
-  if (lut_in_smem) {
-    for (int i = threadIdx.x; i < lut_len; i += blockDim.x) lut_s[i] = lut[i];
-    lut = lut_s;
+  if (lut_in_smem) {   // the group's heads, one after the other
+    for (int i = threadIdx.x; i < rep * lut_len; i += blockDim.x) lut_s[i] = bias_lut[static_cast<int64_t>(g) * rep * lut_len + i];
   }
   const int qc = dk / 8, vc = dvp / 8;          // 16-byte chunks per row
 
-  // Q tile (rows beyond the tile's tokens are zero); element-wise when the rows are not 16-byte aligned
+  // Q tile (rows beyond the tile's are zero); element-wise when the rows are not 16-byte aligned
   if (q_vec) {
     for (int c = threadIdx.x; c < kMmaRows * qc; c += blockDim.x) {
       const int r = c / qc, e = (c - r * qc) * 8;
-      const bool ok = r < tile.count;
-      cp_async16(q_s + r * ldq + e, ok ? q + (tile.tok0 + r) * q_stride + h * dk + e : q, ok);
+      const bool ok = r < n_rows;
+      const int t = r / rep, hh = g * rep + (r - t * rep);
+      cp_async16(q_s + r * ldq + e, ok ? q + (tile.tok0 + t) * q_stride + hh * dk + e : q, ok);
     }
   } else {
     for (int i = threadIdx.x; i < kMmaRows * dk; i += blockDim.x) {
       const int r = i / dk, d = i - r * dk;
-      q_s[r * ldq + d] = r < tile.count ? q[(tile.tok0 + r) * q_stride + h * dk + d] : Cvt<T>::from_f32(0.f);
+      const int t = r / rep, hh = g * rep + (r - t * rep);
+      q_s[r * ldq + d] = r < n_rows ? q[(tile.tok0 + t) * q_stride + hh * dk + d] : Cvt<T>::from_f32(0.f);
     }
   }
   // a thread always moves the same 16-byte column of the rows j = row0, row0 + step, ...: no division per chunk
@@ -480,17 +482,21 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
   cp_async_commit();
 
   const int row_a = warp * 16 + gq;                      // this thread's rows: row_a and row_a + 8
-  int posr[2];
+  int posr[2], headr[2], tokr[2];
+  const float* lut[2];
   float qmul[2], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int r = row_a + 8 * i;
-    posr[i] = r < tile.count ? pos0 + r : -1;
+    tokr[i] = r / rep;
+    headr[i] = g * rep + (r - tokr[i] * rep);
+    posr[i] = r < n_rows ? pos0 + tokr[i] : -1;
+    lut[i] = lut_in_smem ? lut_s + (r - tokr[i] * rep) * lut_len : bias_lut + static_cast<int64_t>(headr[i]) * lut_len;
     const float steps = static_cast<float>((posr[i] + 1) / max(temp_every, 1));
     qmul[i] = scale * (1.0f + temp_coef * logf(steps + 1.0f));
   }
-  const int warp_pos_max = min(pos0 + warp * 16 + 15, pos_last);
-  const bool warp_live = warp * 16 < tile.count;
+  const int warp_pos_max = pos0 + min((warp * 16 + 15) / rep, tile.count - 1);
+  const bool warp_live = warp * 16 < n_rows;
   float o[DV8][4];
 #pragma unroll
   for (int n = 0; n < DV8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -534,7 +540,7 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
           const int i = e >> 1;
           const int key = j0 + n * 8 + 2 * tq + (e & 1);
           float sc = -INFINITY;
-          if (key <= posr[i]) sc = s[n][e] * qmul[i] + lut[min(posr[i] - key, lut_len - 1)];
+          if (key <= posr[i]) sc = s[n][e] * qmul[i] + lut[i][min(posr[i] - key, lut_len - 1)];
           s[n][e] = sc;
           mx[i] = fmaxf(mx[i], sc);
         }
@@ -595,8 +601,9 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
     const int r = row_a + 8 * i;
-    if (r >= tile.count) continue;
-    const int64_t n_tok = tile.tok0 + r;
+    if (r >= n_rows) continue;
+    const int64_t n_tok = tile.tok0 + tokr[i];
+    const int h = headr[i];
     const float gt = gate ? sigmoidf_(Cvt<T>::to_f32(gate[n_tok * gate_stride + h])) : 1.0f;
     const float inv = gt / l[i];
     T* orow = out + (n_tok * H + h) * dv;
@@ -1099,6 +1106,8 @@ int b200_biased_paged_attn(void* out, const void* q, int64_t q_stride, const voi
   });
 }
 
+int b200_biased_prompt_attn_tile_tokens(int H, int G) { return std::max(1, kMmaRows / std::max(1, H / std::max(G, 1))); }
+
 int b200_biased_prompt_attn_supported(int dk, int dv, int dtype) {
   return (dtype == B200_DTYPE_BF16 || dtype == B200_DTYPE_F16) && dk > 0 && dk % 16 == 0 && dk <= 256 && dv > 0 &&
          dv % 8 == 0 && dv <= 128;
@@ -1121,9 +1130,13 @@ int b200_biased_prompt_attn(void* out, const void* q, int64_t q_stride, const vo
   const int q_vec = aligned16(q) && (q_stride * 2) % 16 == 0;
   const int dv8 = dv <= 32 ? 4 : (dv <= 64 ? 8 : 16);
   const size_t tiles_bytes = 2u * (static_cast<size_t>(kMmaRows) * (dk + 8) * 3 + 2u * kMmaKeys * (dv8 * 8 + 8));
-  const int lut_in_smem = static_cast<size_t>(lut_len) * 4 + tiles_bytes <= 200 * 1024 && lut_len <= 16384;
-  const size_t smem = tiles_bytes + (lut_in_smem ? static_cast<size_t>(lut_len) * 4 : 0);
-  const dim3 grid(n_tiles, H);
+  const int rep = H / G;
+  if (rep > kMmaRows) return fail(B200_ESHAPE, "b200_biased_prompt_attn: %d heads per kv head > %d", rep, kMmaRows);
+  // the group's bias tables go to shared memory when they are small enough to leave room for two CTAs per SM
+  const size_t lut_bytes = static_cast<size_t>(rep) * lut_len * 4;
+  const int lut_in_smem = lut_bytes <= 20 * 1024;
+  const size_t smem = tiles_bytes + (lut_in_smem ? lut_bytes : 0);
+  const dim3 grid(n_tiles, G);
   return mixer_by_dtype(dtype, "b200_biased_prompt_attn", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
     if constexpr (std::is_same_v<T, float>) {

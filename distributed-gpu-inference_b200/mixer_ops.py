@@ -140,8 +140,9 @@ def biased_paged_attention(q: torch.Tensor, gate: Optional[torch.Tensor], k_pool
     return out
 
 
-PROMPT_TILE_TOKENS = 64     # tokens of one sequence a CTA of the tensor-core prompt kernel serves
-PROMPT_MIN_TOKENS = 16      # shorter portions (and decoded tokens) go through biased_paged_attention
+def prompt_tile_tokens(H: int, G: int) -> int:
+    """Tokens of one sequence a CTA of the tensor-core kernel serves: 64 rows over the heads of a kv group."""
+    return int(_lib_().b200_biased_prompt_attn_tile_tokens(int(H), int(G)))
 
 
 def prompt_attention_supported(dk: int, dv: int, dtype: torch.dtype) -> bool:
@@ -152,8 +153,9 @@ def prompt_attention_supported(dk: int, dv: int, dtype: torch.dtype) -> bool:
 def biased_prompt_attention(out: torch.Tensor, q: torch.Tensor, gate: Optional[torch.Tensor], k_pool: torch.Tensor,
                             v_pool: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, tok_pos: torch.Tensor,
                             bias_lut: torch.Tensor, scale: float, temp_coef: float, temp_every: int, H: int) -> None:
-    """``biased_paged_attention`` for prompt portions on the tensor cores; writes the tiles' rows of ``out``
-    ``[n, H*dv]`` (16-bit dtypes, see ``prompt_attention_supported``).  ``tiles``: up to 64 tokens each."""
+    """``biased_paged_attention`` on the tensor cores, for prompt portions and decoded tokens alike; writes the tiles'
+    rows of ``out`` ``[n, H*dv]`` (16-bit dtypes, see ``prompt_attention_supported``).  ``tiles``: up to
+    ``prompt_tile_tokens(H, G)`` tokens each."""
     _need_cuda(out, q, k_pool, v_pool, block_tables, tiles, tok_pos, bias_lut)
     nb, G, bs, dk = k_pool.shape
     dv = v_pool.shape[3]

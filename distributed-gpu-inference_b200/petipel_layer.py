@@ -166,14 +166,12 @@ class BiasedPagedAttention(nn.Module):
                                     v_prev=v_prev, lam=self.lam, v_keep=v_keep)
         q, gate = proj[:, :a], proj[:, c:c + H]
         attn = torch.empty((h.shape[0], H * dv), dtype=h.dtype, device=h.device)
-        split = mixer_ops.PROMPT_MIN_TOKENS if self.tensor_core_prompt else 0
-        if split:   # prompt portions: tensor cores; short portions and decoded tokens: the row kernel below
-            tiles, _ = st.prompt_tiles(split, mixer_ops.PROMPT_TILE_TOKENS)
-            if tiles.shape[0]:
-                mixer_ops.biased_prompt_attention(attn, q, gate, cache.k_pool, cache.v_pool, st.block_tables, tiles,
-                                                  st.tok_pos, self.bias_lut, self.scale, self.temp_coef, self.temp_every, H)
-        tiles, most = st.tiles_for(H, G, below=split)
-        if tiles.shape[0]:
+        if self.tensor_core_prompt:   # 16-bit storage and sizes the tensor-core kernel takes: portions and single tokens
+            tiles, _ = st.prompt_tiles(1, mixer_ops.prompt_tile_tokens(H, G))
+            mixer_ops.biased_prompt_attention(attn, q, gate, cache.k_pool, cache.v_pool, st.block_tables, tiles,
+                                              st.tok_pos, self.bias_lut, self.scale, self.temp_coef, self.temp_every, H)
+        else:                         # fp32, or head sizes off the tensor-core grid: the row kernel
+            tiles, most = st.tiles_for(H, G)
             mixer_ops.biased_paged_attention(q, gate, cache.k_pool, cache.v_pool, st.block_tables, tiles, most,
                                              st.tok_pos, self.bias_lut, self.scale, self.temp_coef, self.temp_every, H,
                                              out=attn)

@@ -33,6 +33,9 @@ def test_mixers_library_matches_its_header():
     assert lib.b200_biased_attn_tile_tokens(1000, 4, 1) == 8
     assert lib.b200_biased_attn_tile_tokens(1000, 8, 8) == 32
     assert lib.b200_biased_attn_tile_tokens(1, 4, 1) == 1
+    assert lib.b200_biased_prompt_attn_tile_tokens(16, 4) == 16 and lib.b200_biased_prompt_attn_tile_tokens(6, 6) == 64
+    assert lib.b200_biased_prompt_attn_supported(96, 32, 2) == 1 and lib.b200_biased_prompt_attn_supported(96, 32, 1) == 0
+    assert lib.b200_biased_prompt_attn_supported(20, 48, 2) == 0
     rc = lib.b200_polynorm(None, None, 0, None, 1e-6, 4, 8, 7, None)  # dtype 7
     assert rc == -1 and b"null pointer" in lib.b200_mixers_last_error()
     rc = lib.b200_gated_scan(None, None, None, None, 0, None, None, None, None, 1, 1, 0, 4, 4, 2, None)

@@ -501,10 +501,11 @@ def test_prompt_kernel_finds_needles_and_respects_edges(dtype, H, G, dk, dv):
     kr, vr = k.to(dtype).float(), v.to(dtype).float()
     ref = _attention_rows(qd.float().view(n_ctx, H, dk), gd.float(), kr, vr, list(range(n_ctx)), rel, far, 0.3, coef,
                           every, H, G)
-    for lo, n in ((0, n_ctx), (0, 17), (37, 150), (250, 83), (317, 16)):
+    for lo, n in ((0, n_ctx), (0, 17), (37, 150), (250, 83), (317, 16), (332, 1), (64, 1), (0, 1), (130, 3)):
         out = torch.full((n, H * dv), 7.0, dtype=dtype, device=DEV)
         M.biased_prompt_attention(out, qd[lo:lo + n].to(DEV), gd[lo:lo + n].to(DEV), k_pool.to(DEV, dtype),
-                                  v_pool.to(DEV, dtype), table.to(DEV), _prompt_tiles([(0, n, 0)]).to(DEV),
+                                  v_pool.to(DEV, dtype), table.to(DEV),
+                                  _prompt_tiles([(0, n, 0)], M.prompt_tile_tokens(H, G)).to(DEV),
                                   torch.arange(lo, lo + n, dtype=torch.int32, device=DEV), lut.to(DEV), 0.3, coef, every, H)
         close(out.float().cpu(), ref[lo:lo + n], 2.5e-2)
 
@@ -529,7 +530,8 @@ def test_prompt_kernel_two_sequences_and_unaligned_rows():
     lut = torch.zeros(H, 5)
     out = torch.empty(170, H * dv, dtype=torch.bfloat16, device=DEV)
     M.biased_prompt_attention(out, wide.to(DEV)[:, :H * dk], None, k_pool.to(DEV, torch.bfloat16),
-                              v_pool.to(DEV, torch.bfloat16), table.to(DEV), _prompt_tiles([(0, 70, 0), (70, 100, 1)]).to(DEV),
+                              v_pool.to(DEV, torch.bfloat16), table.to(DEV),
+                              _prompt_tiles([(0, 70, 0), (70, 100, 1)], M.prompt_tile_tokens(H, G)).to(DEV),
                               pos.to(DEV), lut.to(DEV), 0.2, 0.0, 1, H)
     big = torch.full((170, H), 30.0)
     rel = torch.zeros(4, H)
