@@ -115,7 +115,8 @@ MIXER_SIGNATURES = {
     "b200_biased_prompt_attn_tile_tokens": (c_int, [c_int, c_int]),
     "b200_biased_prompt_attn": (
         c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                c_int, c_void_p, c_void_p, c_int, c_float, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                c_void_p]),
     "b200_gated_scan": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                 c_int, c_int, c_int, c_int, c_void_p]),

@@ -407,7 +407,9 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 constexpr int kMmaRows = 64;   // query rows per CTA
 constexpr int kMmaKeys = 64;   // keys per tile
 
-template <typename T, int DV8>
+// KSPLIT (tiles of at most 16 rows, i.e. decoded tokens): all four warps work on the SAME 16 rows and each takes 16
+// of a tile's 64 keys; their running (max, sum, output) are merged through shared memory at the end.
+template <typename T, int DV8, bool KSPLIT>
 __global__ void __launch_bounds__(128)
 biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q_stride, const T* __restrict__ gate,
                               int64_t gate_stride, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
@@ -481,7 +483,7 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
   load_kv(0, 0);
   cp_async_commit();
 
-  const int row_a = warp * 16 + gq;                      // this thread's rows: row_a and row_a + 8
+  const int row_a = (KSPLIT ? 0 : warp * 16) + gq;       // this thread's rows: row_a and row_a + 8
   int posr[2], headr[2], tokr[2];
   const float* lut[2];
   float qmul[2], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -495,8 +497,10 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
     const float steps = static_cast<float>((posr[i] + 1) / max(temp_every, 1));
     qmul[i] = scale * (1.0f + temp_coef * logf(steps + 1.0f));
   }
-  const int warp_pos_max = pos0 + min((warp * 16 + 15) / rep, tile.count - 1);
-  const bool warp_live = warp * 16 < n_rows;
+  const int warp_pos_max = KSPLIT ? pos_last : pos0 + min((warp * 16 + 15) / rep, tile.count - 1);
+  const bool warp_live = KSPLIT || warp * 16 < n_rows;
+  constexpr int NT = KSPLIT ? 2 : 8;                     // 8-key n-tiles of a key tile this warp scores
+  const int nt0 = KSPLIT ? 2 * warp : 0;
   float o[DV8][4];
 #pragma unroll
   for (int n = 0; n < DV8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -515,9 +519,9 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
     if (warp_live && j0 <= warp_pos_max) {
       const T* kt = k_s + (it & 1) * kMmaKeys * ldq;
       const T* vt = v_s + (it & 1) * kMmaKeys * ldv;
-      float s[8][4];
+      float s[NT][4];
 #pragma unroll
-      for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+      for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
       for (int kk = 0; kk < dk / 16; ++kk) {
         uint32_t a[4];
         const T* qa = q_s + row_a * ldq + kk * 16 + 2 * tq;
@@ -526,19 +530,19 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
         a[2] = *reinterpret_cast<const uint32_t*>(qa + 8);
         a[3] = *reinterpret_cast<const uint32_t*>(qa + 8 * ldq + 8);
 #pragma unroll
-        for (int n = 0; n < 8; ++n) {
-          const T* kb = kt + (n * 8 + gq) * ldq + kk * 16 + 2 * tq;
+        for (int n = 0; n < NT; ++n) {
+          const T* kb = kt + ((nt0 + n) * 8 + gq) * ldq + kk * 16 + 2 * tq;
           Mma16<T>::mma(s[n], a, *reinterpret_cast<const uint32_t*>(kb), *reinterpret_cast<const uint32_t*>(kb + 8));
         }
       }
-      // fp32 softmax on the fragments: element e of s[n] is (row gq + 8 (e >> 1), key 8 n + 2 tq + (e & 1))
+      // fp32 softmax on the fragments: element e of s[n] is (row gq + 8 (e >> 1), key 8 (nt0 + n) + 2 tq + (e & 1))
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
+      for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int i = e >> 1;
-          const int key = j0 + n * 8 + 2 * tq + (e & 1);
+          const int key = j0 + (nt0 + n) * 8 + 2 * tq + (e & 1);
           float sc = -INFINITY;
           if (key <= posr[i]) sc = s[n][e] * qmul[i] + lut[i][min(posr[i] - key, lut_len - 1)];
           s[n][e] = sc;
@@ -557,7 +561,7 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
       }
       float part[2] = {0.f, 0.f};
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
+      for (int n = 0; n < NT; ++n) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float pexp = expf(s[n][e] - msafe[e >> 1]);
@@ -575,15 +579,16 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
         o[n][3] *= corr[1];
       }
 #pragma unroll
-      for (int k2 = 0; k2 < kMmaKeys / 16; ++k2) {
+      for (int k2 = 0; k2 < NT / 2; ++k2) {
         uint32_t a[4];
         a[0] = Mma16<T>::pack(s[2 * k2][0], s[2 * k2][1]);
         a[1] = Mma16<T>::pack(s[2 * k2][2], s[2 * k2][3]);
         a[2] = Mma16<T>::pack(s[2 * k2 + 1][0], s[2 * k2 + 1][1]);
         a[3] = Mma16<T>::pack(s[2 * k2 + 1][2], s[2 * k2 + 1][3]);
+        const int key16 = (nt0 / 2 + k2) * 16;           // first key (within the tile) of this 16-key step
 #pragma unroll
         for (int n = 0; n < DV8; n += 2) {
-          const T* vrow = vt + (k2 * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + n * 8 + (lane >> 4) * 8;
+          const T* vrow = vt + (key16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldv + n * 8 + (lane >> 4) * 8;
           const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(vrow));
           uint32_t b0, b1, b2, b3;
           asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -600,6 +605,51 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
   for (int i = 0; i < 2; ++i) {
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 1);
     l[i] += __shfl_xor_sync(0xffffffffu, l[i], 2);
+  }
+  if constexpr (KSPLIT) {
+    // merge the four warps' partial results for the 16 shared rows: every warp rescales its own to the common
+    // maximum and the sums are taken warp 0, 1, 2, 3 in order; the K / V stages are free now
+    float* mg = reinterpret_cast<float*>(k_s);            // [4 warps][16 rows] maxima, then [4][16] sums
+    float* og = mg + 128;                                  // [4 warps][16 rows][dvp]
+    if (tq == 0) {
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        mg[warp * 16 + gq + 8 * i] = m[i];
+        mg[64 + warp * 16 + gq + 8 * i] = l[i];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = gq + 8 * i;
+      float mall = fmaxf(fmaxf(mg[r], mg[16 + r]), fmaxf(mg[32 + r], mg[48 + r]));
+      mall = mall == -INFINITY ? 0.f : mall;
+      const float w = expf(m[i] - mall);                  // this warp's weight in the merge
+      float lsum = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < 4; ++w2) lsum += mg[64 + w2 * 16 + r] * expf(mg[w2 * 16 + r] - mall);
+      l[i] = lsum;
+#pragma unroll
+      for (int n = 0; n < DV8; ++n) {
+        og[(warp * 16 + r) * dvp + n * 8 + 2 * tq] = o[n][2 * i] * w;
+        og[(warp * 16 + r) * dvp + n * 8 + 2 * tq + 1] = o[n][2 * i + 1] * w;
+      }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = gq + 8 * i;
+#pragma unroll
+      for (int n = 0; n < DV8; ++n) {
+        const int c = n * 8 + 2 * tq;
+        o[n][2 * i] = (og[r * dvp + c] + og[(16 + r) * dvp + c]) + (og[(32 + r) * dvp + c] + og[(48 + r) * dvp + c]);
+        o[n][2 * i + 1] = (og[r * dvp + c + 1] + og[(16 + r) * dvp + c + 1]) + (og[(32 + r) * dvp + c + 1] + og[(48 + r) * dvp + c + 1]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
     const int r = row_a + 8 * i;
     if (r >= n_rows) continue;
     const int64_t n_tok = tile.tok0 + tokr[i];
@@ -1115,7 +1165,7 @@ int b200_biased_prompt_attn_supported(int dk, int dv, int dtype) {
 
 int b200_biased_prompt_attn(void* out, const void* q, int64_t q_stride, const void* gate, int64_t gate_stride,
                             const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
-                            const int32_t* tiles, int n_tiles, const int32_t* tok_pos, const float* bias_lut,
+                            const int32_t* tiles, int n_tiles, int max_tile_tokens, const int32_t* tok_pos, const float* bias_lut,
                             int lut_len, float scale, float temp_coef, int temp_every, int H, int G, int dk, int dv,
                             int block_size, int dtype, void* stream) {
   if (n_tiles < 0 || H <= 0 || G <= 0 || H % G || block_size <= 0 || lut_len <= 0)
@@ -1150,9 +1200,17 @@ int b200_biased_prompt_attn(void* out, const void* q, int64_t q_stride, const vo
             reinterpret_cast<const AttnTile*>(tiles), tok_pos, bias_lut, lut_len, lut_in_smem, q_vec, scale, temp_coef,
             temp_every, H, G, dk, dv, block_size);
       };
-      if (dv8 == 4) launch(biased_prompt_attn_mma_kernel<T, 4>);
-      else if (dv8 == 8) launch(biased_prompt_attn_mma_kernel<T, 8>);
-      else launch(biased_prompt_attn_mma_kernel<T, 16>);
+      // tiles of at most 16 rows (decoded tokens): the four warps split the keys instead of the rows
+      const bool ksplit = max_tile_tokens > 0 && max_tile_tokens * rep <= 16;
+      if (ksplit) {
+        if (dv8 == 4) launch(biased_prompt_attn_mma_kernel<T, 4, true>);
+        else if (dv8 == 8) launch(biased_prompt_attn_mma_kernel<T, 8, true>);
+        else launch(biased_prompt_attn_mma_kernel<T, 16, true>);
+      } else {
+        if (dv8 == 4) launch(biased_prompt_attn_mma_kernel<T, 4, false>);
+        else if (dv8 == 8) launch(biased_prompt_attn_mma_kernel<T, 8, false>);
+        else launch(biased_prompt_attn_mma_kernel<T, 16, false>);
+      }
       return check_launch("b200_biased_prompt_attn");
     }
   });

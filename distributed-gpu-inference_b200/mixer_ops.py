@@ -152,10 +152,12 @@ def prompt_attention_supported(dk: int, dv: int, dtype: torch.dtype) -> bool:
 @_timed
 def biased_prompt_attention(out: torch.Tensor, q: torch.Tensor, gate: Optional[torch.Tensor], k_pool: torch.Tensor,
                             v_pool: torch.Tensor, block_tables: torch.Tensor, tiles: torch.Tensor, tok_pos: torch.Tensor,
-                            bias_lut: torch.Tensor, scale: float, temp_coef: float, temp_every: int, H: int) -> None:
+                            bias_lut: torch.Tensor, scale: float, temp_coef: float, temp_every: int, H: int,
+                            max_tile_tokens: int = 0) -> None:
     """``biased_paged_attention`` on the tensor cores, for prompt portions and decoded tokens alike; writes the tiles'
     rows of ``out`` ``[n, H*dv]`` (16-bit dtypes, see ``prompt_attention_supported``).  ``tiles``: up to
-    ``prompt_tile_tokens(H, G)`` tokens each."""
+    ``prompt_tile_tokens(H, G)`` tokens each; ``max_tile_tokens``: the largest tile (0 = unknown) — steps of decoded
+    tokens only take the variant whose warps split the keys."""
     _need_cuda(out, q, k_pool, v_pool, block_tables, tiles, tok_pos, bias_lut)
     nb, G, bs, dk = k_pool.shape
     dv = v_pool.shape[3]
@@ -171,7 +173,7 @@ def biased_prompt_attention(out: torch.Tensor, q: torch.Tensor, gate: Optional[t
     rc = _lib_().b200_biased_prompt_attn(out.data_ptr(), q.data_ptr(), _rows2(q), _ptr(gate),
                                          _rows2(gate) if gate is not None else 0, k_pool.data_ptr(), v_pool.data_ptr(),
                                          block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(), tiles.shape[0],
-                                         tok_pos.data_ptr(), bias_lut.data_ptr(), bias_lut.shape[1], float(scale),
+                                         int(max_tile_tokens), tok_pos.data_ptr(), bias_lut.data_ptr(), bias_lut.shape[1], float(scale),
                                          float(temp_coef), int(temp_every), H, G, dk, dv, bs, DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_biased_prompt_attn")
 

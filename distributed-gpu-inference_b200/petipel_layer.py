@@ -167,9 +167,10 @@ class BiasedPagedAttention(nn.Module):
         q, gate = proj[:, :a], proj[:, c:c + H]
         attn = torch.empty((h.shape[0], H * dv), dtype=h.dtype, device=h.device)
         if self.tensor_core_prompt:   # 16-bit storage and sizes the tensor-core kernel takes: portions and single tokens
-            tiles, _ = st.prompt_tiles(1, mixer_ops.prompt_tile_tokens(H, G))
+            tiles, most = st.prompt_tiles(1, mixer_ops.prompt_tile_tokens(H, G))
             mixer_ops.biased_prompt_attention(attn, q, gate, cache.k_pool, cache.v_pool, st.block_tables, tiles,
-                                              st.tok_pos, self.bias_lut, self.scale, self.temp_coef, self.temp_every, H)
+                                              st.tok_pos, self.bias_lut, self.scale, self.temp_coef, self.temp_every, H,
+                                              max_tile_tokens=most)
         else:                         # fp32, or head sizes off the tensor-core grid: the row kernel
             tiles, most = st.tiles_for(H, G)
             mixer_ops.biased_paged_attention(q, gate, cache.k_pool, cache.v_pool, st.block_tables, tiles, most,

@@ -60,15 +60,17 @@ int b200_biased_paged_attn(void* out, const void* q, int64_t q_stride, const voi
 /* The same attention on the tensor cores (16-bit dtypes; dk a multiple of 16 up to 256, dv a multiple of 8 up to
  * 128 — b200_biased_prompt_attn_supported says whether a layer qualifies).  A CTA serves 64 rows = the tokens of a tile
  * times the query heads of one kv head, so tiles hold up to b200_biased_prompt_attn_tile_tokens(H, G) = 64 / (H / G)
- * tokens; a tile's tokens have consecutive positions.  Prompt portions and single decoded tokens alike.  Scores, bias and softmax are fp32; the softmax
+ * tokens; a tile's tokens have consecutive positions.  Prompt portions and single decoded tokens alike: when no tile
+ * has more than max_tile_tokens tokens and that many tokens are at most 16 rows, the warps of a CTA split the keys
+ * instead of the rows (pass 0 when unknown).  Scores, bias and softmax are fp32; the softmax
  * weights are rounded to the storage type only as the operand of the P.V product.  Rows written: the tiles' tokens. */
 int b200_biased_prompt_attn_supported(int dk, int dv, int dtype);
 int b200_biased_prompt_attn_tile_tokens(int H, int G);
 int b200_biased_prompt_attn(void* out, const void* q, int64_t q_stride, const void* gate, int64_t gate_stride,
                             const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
-                            const int32_t* tiles, int n_tiles, const int32_t* tok_pos, const float* bias_lut,
-                            int lut_len, float scale, float temp_coef, int temp_every, int H, int G, int dk, int dv,
-                            int block_size, int dtype, void* stream);
+                            const int32_t* tiles, int n_tiles, int max_tile_tokens, const int32_t* tok_pos,
+                            const float* bias_lut, int lut_len, float scale, float temp_coef, int temp_every, int H, int G,
+                            int dk, int dv, int block_size, int dtype, void* stream);
 
 /* Gated linear recurrence per (sequence, head) over the sequence's tokens of this step, in order:
  *   q = silu(zq), f = lower + (1 - lower) * sigmoid(zf + f_bias), S <- diag(f) S + (1 - f) v^T, o = S^T q.

@@ -506,7 +506,8 @@ def test_prompt_kernel_finds_needles_and_respects_edges(dtype, H, G, dk, dv):
         M.biased_prompt_attention(out, qd[lo:lo + n].to(DEV), gd[lo:lo + n].to(DEV), k_pool.to(DEV, dtype),
                                   v_pool.to(DEV, dtype), table.to(DEV),
                                   _prompt_tiles([(0, n, 0)], M.prompt_tile_tokens(H, G)).to(DEV),
-                                  torch.arange(lo, lo + n, dtype=torch.int32, device=DEV), lut.to(DEV), 0.3, coef, every, H)
+                                  torch.arange(lo, lo + n, dtype=torch.int32, device=DEV), lut.to(DEV), 0.3, coef, every, H,
+                                  max_tile_tokens=min(n, M.prompt_tile_tokens(H, G)))   # <= 16 rows: the key-split variant
         close(out.float().cpu(), ref[lo:lo + n], 2.5e-2)
 
 
