@@ -178,6 +178,8 @@ def _kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> Dict[str,
             "value_prep_append": (n_tok * G * (dk + dv) * 2 * 2 + n_tok * G * dv * 2, 0),
             "biased_paged_attention": (n_seq * (past + per_seq) * G * (dk + dv) * 2 + n_tok * H * (dk + dv) * 2,
                                        n_seq * H * 2 * (dk + dv) * (per_seq * past + per_seq * (per_seq + 1) // 2)),
+            "biased_prompt_attention": (n_seq * (past + per_seq) * G * (dk + dv) * 2 + n_tok * H * (dk + dv) * 2,
+                                        n_seq * H * 2 * (dk + dv) * (per_seq * past + per_seq * (per_seq + 1) // 2)),
             "gated_scan": (n_tok * RH * (2 * rdk + rdv) * 2 + n_tok * RH * rdv * 4 + 2 * n_seq * RH * rdk * rdv * 4, 0),
             "head_rmsnorm": (n_tok * RH * rdv * 6, 0),
             "polynorm": (n_tok * s["ff"] * 4, 0),
