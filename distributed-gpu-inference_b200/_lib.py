@@ -124,6 +124,8 @@ MIXER_SIGNATURES = {
     "b200_polynorm": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_float, c_int, c_int, c_int, c_void_p]),
     "b200_sigmoid_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200_scaled_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_grouped_linear_supported": (c_int, [c_int, c_int]),
+    "b200_grouped_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_clamped_glu": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_float, c_float, c_int, c_void_p]),
     "b200_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
 }

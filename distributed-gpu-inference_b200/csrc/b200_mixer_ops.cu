@@ -668,6 +668,89 @@ biased_prompt_attn_mma_kernel(T* __restrict__ out, const T* __restrict__ q, int6
   }
 }
 
+// ---- grouped linear for expert-sorted rows (16-bit storage) ---------------------------------------------------------
+// out[r] = xs[r] . w[e]^T for the rows offsets[e] <= r < offsets[e + 1]; the offsets stay on the device, so routing
+// needs no copy to the host and all experts run in one launch.  CTA = 16 rows x 256 output columns of one expert
+// (each of 4 warps: 16 x 64 with mma.sync m16n8k16, fp32 accumulators); K in chunks of 64 by cp.async, two stages.
+// CTAs whose row tile lies beyond their expert's rows leave at once.
+constexpr int kGrpRows = 16, kGrpCols = 256, kGrpK = 64;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+grouped_linear_kernel(T* __restrict__ out, const T* __restrict__ xs, const T* __restrict__ w,
+                      const int32_t* __restrict__ offsets, int N, int K) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int e = blockIdx.y;
+  const int row0 = offsets[e] + blockIdx.z * kGrpRows;
+  const int row_end = offsets[e + 1];
+  if (row0 >= row_end) return;
+  const int n0 = blockIdx.x * kGrpCols;
+  constexpr int ld = kGrpK + 8;
+  T* x_s = reinterpret_cast<T*>(smem_raw);            // 2 x [16][ld]
+  T* w_s = x_s + 2 * kGrpRows * ld;                   // 2 x [256][ld]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+  const T* wbase = w + static_cast<int64_t>(e) * N * K;
+  auto load = [&](int kc, int stage) {
+    {
+      const int r = threadIdx.x >> 3, e8 = (threadIdx.x & 7) * 8;
+      const bool ok = row0 + r < row_end && kc + e8 < K;
+      cp_async16(x_s + (stage * kGrpRows + r) * ld + e8, ok ? xs + static_cast<int64_t>(row0 + r) * K + kc + e8 : xs, ok);
+    }
+#pragma unroll 4
+    for (int i = 0; i < kGrpCols * 8 / 128; ++i) {
+      const int c = threadIdx.x + i * 128;
+      const int n = c >> 3, e8 = (c & 7) * 8;
+      const bool ok = n0 + n < N && kc + e8 < K;
+      cp_async16(w_s + (stage * kGrpCols + n) * ld + e8, ok ? wbase + static_cast<int64_t>(n0 + n) * K + kc + e8 : wbase, ok);
+    }
+  };
+  float acc[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n) acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f;
+  const int n_kc = (K + kGrpK - 1) / kGrpK;
+  load(0, 0);
+  cp_async_commit();
+  for (int it = 0; it < n_kc; ++it) {
+    if (it + 1 < n_kc) {
+      load((it + 1) * kGrpK, (it + 1) & 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const T* xt = x_s + (it & 1) * kGrpRows * ld;
+    const T* wt = w_s + ((it & 1) * kGrpCols + warp * 64) * ld;
+#pragma unroll
+    for (int kk = 0; kk < kGrpK / 16; ++kk) {
+      uint32_t a[4];
+      const T* xa = xt + gq * ld + kk * 16 + 2 * tq;
+      a[0] = *reinterpret_cast<const uint32_t*>(xa);
+      a[1] = *reinterpret_cast<const uint32_t*>(xa + 8 * ld);
+      a[2] = *reinterpret_cast<const uint32_t*>(xa + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(xa + 8 * ld + 8);
+#pragma unroll
+      for (int n = 0; n < 8; ++n) {
+        const T* wb = wt + (n * 8 + gq) * ld + kk * 16 + 2 * tq;
+        Mma16<T>::mma(acc[n], a, *reinterpret_cast<const uint32_t*>(wb), *reinterpret_cast<const uint32_t*>(wb + 8));
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int r = row0 + gq + 8 * i;
+    if (r >= row_end) continue;
+    T* orow = out + static_cast<int64_t>(r) * N;
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int col = n0 + warp * 64 + n * 8 + 2 * tq;
+      if (col < N) orow[col] = Cvt<T>::from_f32(acc[n][2 * i]);
+      if (col + 1 < N) orow[col + 1] = Cvt<T>::from_f32(acc[n][2 * i + 1]);
+    }
+  }
+}
+
 // ---- gated linear recurrence ------------------------------------------------------------------------------------
 // One CTA per (sequence, head).  The state [dk][dv] lives in shared memory for the whole portion; thread (rg, c)
 // owns column c and the rows i = rg, rg + RG, ...  Inputs of token t + 1 are fetched while token t is computed.
@@ -1212,6 +1295,36 @@ int b200_biased_prompt_attn(void* out, const void* q, int64_t q_stride, const vo
         else launch(biased_prompt_attn_mma_kernel<T, 16, false>);
       }
       return check_launch("b200_biased_prompt_attn");
+    }
+  });
+}
+
+int b200_grouped_linear_supported(int K, int dtype) {
+  return (dtype == B200_DTYPE_BF16 || dtype == B200_DTYPE_F16) && K > 0 && K % 8 == 0;
+}
+
+int b200_grouped_linear(void* out, const void* xs, const void* w, const int32_t* offsets, int64_t max_rows, int E, int N,
+                        int K, int dtype, void* stream) {
+  if (max_rows < 0 || E <= 0 || N <= 0 || K <= 0) return fail(B200_EINVAL, "b200_grouped_linear: bad sizes");
+  if (!b200_grouped_linear_supported(K, dtype))
+    return fail(B200_ESHAPE, "b200_grouped_linear: needs a 16-bit dtype and K %% 8 == 0");
+  if (max_rows == 0) return 0;
+  if (!out || !xs || !w || !offsets) return fail(B200_EINVAL, "b200_grouped_linear: null pointer");
+  if (!aligned16(xs) || !aligned16(w)) return fail(B200_ESHAPE, "b200_grouped_linear: operands must be 16-byte aligned");
+  const int64_t zt = (max_rows + kGrpRows - 1) / kGrpRows;
+  if (zt > 65535 || E > 65535) return fail(B200_ENOSPC, "b200_grouped_linear: %lld row tiles / %d experts beyond the grid", static_cast<long long>(zt), E);
+  const size_t smem = 2u * 2u * (kGrpRows + kGrpCols) * (kGrpK + 8);
+  const dim3 grid((N + kGrpCols - 1) / kGrpCols, E, static_cast<unsigned>(zt));
+  return mixer_by_dtype(dtype, "b200_grouped_linear", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    if constexpr (std::is_same_v<T, float>) {
+      return fail(B200_ESHAPE, "b200_grouped_linear: 16-bit dtypes only");
+    } else {
+      auto kern = grouped_linear_kernel<T>;
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      kern<<<grid, 128, smem, static_cast<cudaStream_t>(stream)>>>(static_cast<T*>(out), static_cast<const T*>(xs),
+                                                                  static_cast<const T*>(w), offsets, N, K);
+      return check_launch("b200_grouped_linear");
     }
   });
 }

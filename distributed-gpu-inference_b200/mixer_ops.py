@@ -255,6 +255,27 @@ def scaled_gather(h: torch.Tensor, weights: torch.Tensor, src: torch.Tensor, top
     return xs
 
 
+def grouped_linear_supported(K: int, dtype: torch.dtype) -> bool:
+    return bool(_lib_().b200_grouped_linear_supported(int(K), DTYPE_ID[dtype]))
+
+
+@_timed
+def grouped_linear(xs: torch.Tensor, w: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """``out[r] = xs[r] @ w[e].T`` for ``offsets[e] <= r < offsets[e + 1]``: ``xs [rows, K]`` sorted by expert,
+    ``w [E, N, K]``, ``offsets`` int32 ``[E + 1]`` on the device (no host copy).  16-bit dtypes."""
+    _need_cuda(xs, w, offsets)
+    E, N, K = w.shape
+    if xs.dim() != 2 or xs.shape[1] != K or not xs.is_contiguous() or not w.is_contiguous() or xs.dtype != w.dtype:
+        raise ValueError("xs [rows, K] and w [E, N, K] must be contiguous and of one dtype")
+    if offsets.dtype != torch.int32 or offsets.numel() != E + 1 or not offsets.is_contiguous():
+        raise ValueError("offsets must be contiguous int32 [E + 1]")
+    out = torch.empty((xs.shape[0], N), dtype=xs.dtype, device=xs.device)
+    rc = _lib_().b200_grouped_linear(out.data_ptr(), xs.data_ptr(), w.data_ptr(), offsets.data_ptr(), xs.shape[0], E, N, K,
+                                     DTYPE_ID[xs.dtype], _stream())
+    _lib.check_mixers(rc, "b200_grouped_linear")
+    return out
+
+
 @_timed
 def clamped_glu(gu: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
     _need_cuda(gu)

@@ -217,6 +217,7 @@ class SigmoidTopKMoE(nn.Module):
     clamped GLUs and summed per token in fp32.  ``GLU_ALPHA`` is fixed by the design."""
 
     GLU_ALPHA = 1.702
+    GROUPED_MAX_ROWS = 2048     # routed rows of a step up to which the grouped kernel beats per-expert vendor GEMMs
 
     def __init__(self, spec: Dict[str, Any], t: Dict[str, torch.Tensor], device, dtype):
         super().__init__()
@@ -226,27 +227,38 @@ class SigmoidTopKMoE(nn.Module):
         self.w_gu = _param(torch.stack([torch.cat([t[f"e{e}.gate"], t[f"e{e}.up"]], dim=0) for e in range(self.E)]),
                            device, dtype)                                                    # [E, 2 ff, W]
         self.w_down = _param(torch.stack([t[f"e{e}.down"] for e in range(self.E)]), device, dtype)  # [E, W, ff]
+        self.grouped = (mixer_ops.grouped_linear_supported(self.w_gu.shape[2], self.w_gu.dtype)
+                        and mixer_ops.grouped_linear_supported(self.w_down.shape[2], self.w_down.dtype))
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         n, top = h.shape[0], self.top
         ids, w = mixer_ops.sigmoid_topk(F.linear(h.to(torch.float32), self.w_router), top)
         flat = ids.reshape(-1).to(torch.int64)
         order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=self.E).tolist()
+        counts = torch.bincount(flat, minlength=self.E)
         xs = mixer_ops.scaled_gather(h, w.reshape(-1), order, top)
-        gu = torch.empty((n * top, self.w_gu.shape[1]), dtype=h.dtype, device=h.device)
-        lo = 0
-        for e, c in enumerate(counts):
-            if c:
-                torch.mm(xs[lo:lo + c], self.w_gu[e].t(), out=gu[lo:lo + c])
-                lo += c
-        y = mixer_ops.clamped_glu(gu, self.limit, self.GLU_ALPHA)
-        ys = torch.empty((n * top, h.shape[1]), dtype=h.dtype, device=h.device)
-        lo = 0
-        for e, c in enumerate(counts):
-            if c:
-                torch.mm(y[lo:lo + c], self.w_down[e].t(), out=ys[lo:lo + c])
-                lo += c
+        if self.grouped and n * top <= self.GROUPED_MAX_ROWS:
+            # all experts in one launch each way, offsets stay on the device: no host copy, no per-expert calls
+            offsets = torch.zeros(self.E + 1, dtype=torch.int32, device=h.device)
+            offsets[1:] = torch.cumsum(counts, 0)
+            y = mixer_ops.clamped_glu(mixer_ops.grouped_linear(xs, self.w_gu, offsets), self.limit, self.GLU_ALPHA)
+            ys = mixer_ops.grouped_linear(y, self.w_down, offsets)
+        else:
+            # long prompt steps (and fp32): one vendor GEMM per expert each way; the counts come to the host once
+            counts = counts.tolist()
+            gu = torch.empty((n * top, self.w_gu.shape[1]), dtype=h.dtype, device=h.device)
+            lo = 0
+            for e, c in enumerate(counts):
+                if c:
+                    torch.mm(xs[lo:lo + c], self.w_gu[e].t(), out=gu[lo:lo + c])
+                    lo += c
+            y = mixer_ops.clamped_glu(gu, self.limit, self.GLU_ALPHA)
+            ys = torch.empty((n * top, h.shape[1]), dtype=h.dtype, device=h.device)
+            lo = 0
+            for e, c in enumerate(counts):
+                if c:
+                    torch.mm(y[lo:lo + c], self.w_down[e].t(), out=ys[lo:lo + c])
+                    lo += c
         where = torch.empty_like(order)
         where[order] = torch.arange(n * top, device=h.device)
         return mixer_ops.expert_combine(ys, where, n, top)

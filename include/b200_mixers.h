@@ -97,6 +97,13 @@ int b200_sigmoid_topk(int32_t* ids, float* weights, const float* logits, int n_t
 int b200_scaled_gather(void* xs, const void* h, const float* weights, const int64_t* src, int64_t n_rows, int top,
                        int width, int dtype, void* stream);
 
+/* Grouped linear over expert-sorted rows (16-bit dtypes, K a multiple of 8): out[r] = xs[r] . w[e]^T for
+ * offsets[e] <= r < offsets[e + 1].  xs T [rows, K], w T [E, N, K], offsets int32 [E + 1] ON THE DEVICE, out T [rows, N].
+ * max_rows: a bound on the rows of any one expert (the total row count will do); it sizes the grid only. */
+int b200_grouped_linear_supported(int K, int dtype);
+int b200_grouped_linear(void* out, const void* xs, const void* w, const int32_t* offsets, int64_t max_rows, int E, int N,
+                        int K, int dtype, void* stream);
+
 /* y = g' * sigmoid(alpha * g') * (u' + 1), g' = min(g, limit), u' = clamp(u, -limit, limit); gu rows = g | u. */
 int b200_clamped_glu(void* y, const void* gu, int64_t rows, int ff, float limit, float alpha, int dtype, void* stream);
 

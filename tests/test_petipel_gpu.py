@@ -576,3 +576,47 @@ def test_bfloat16_model_with_tensor_core_prompts():
     assert at == 150 and rel(torch.cat(outs).cpu(), ref) < 0.05 and rel(torch.cat(outs).cpu(), got) < 0.04
     eng32, _ = build(CFG_C, dtype=torch.float32)
     close(whole(eng32, "c", toks), ref, 5e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_grouped_linear_with_device_offsets(dtype):
+    """Expert-sorted rows through all experts in one launch: empty experts, an expert with more rows than a row tile,
+    output and inner sizes that are not multiples of the kernel's tiles."""
+    from dgi_b200 import mixer_ops as M
+
+    g = torch.Generator().manual_seed(31)
+    E, N, K = 6, 328, 40
+    counts = [0, 3, 37, 0, 16, 1]
+    rows = sum(counts)
+    xs = torch.randn(rows, K, generator=g).to(dtype)
+    w = (torch.randn(E, N, K, generator=g) / K ** 0.5).to(dtype)
+    offsets = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32)
+    assert M.grouped_linear_supported(K, dtype) and not M.grouped_linear_supported(K, torch.float32)
+    assert not M.grouped_linear_supported(K + 4, dtype)
+    out = M.grouped_linear(xs.to(DEV), w.to(DEV), offsets.to(DEV)).float().cpu()
+    lo = 0
+    for e, c in enumerate(counts):
+        if c:
+            close(out[lo:lo + c], xs[lo:lo + c].float() @ w[e].float().t(), 1e-2)
+        lo += c
+
+
+def test_routed_feed_forward_16_bit_takes_the_grouped_kernel():
+    from dgi_b200 import petipel_layer as P
+
+    g = torch.Generator().manual_seed(32)
+    W, E, ff = 64, 5, 24
+    spec = moe(E, 2, ff=ff, limit=1.5)
+    t = {"router": torch.randn(E, W, generator=g).bfloat16()}
+    for e in range(E):
+        t[f"e{e}.gate"], t[f"e{e}.up"] = (torch.randn(ff, W, generator=g) / 8).bfloat16(), (torch.randn(ff, W, generator=g) / 8).bfloat16()
+        t[f"e{e}.down"] = (torch.randn(W, ff, generator=g) / 5).bfloat16()
+    mod = P.SigmoidTopKMoE(spec, t, DEV, torch.bfloat16)
+    assert mod.grouped
+    h = torch.randn(50, W, generator=g).bfloat16()
+    ref = R.moe_ff(h.float(), {k: v.float() for k, v in t.items()}, spec)
+    got = mod(h.to(DEV)).cpu()
+    mod.GROUPED_MAX_ROWS = 0                      # the per-expert path on the same input
+    loops = mod(h.to(DEV)).cpu()
+    close(got, ref, 2e-2)
+    close(loops, ref, 2e-2)
