@@ -59,6 +59,22 @@ class PagedLLMEngine:
     # ---- BaseEngine ------------------------------------------------------------------------------------------
     def load_model(self) -> None:
         cfg = self.config
+        if cfg.get("model_path"):
+            # a checkpoint folder (config.json + model.safetensors): the model registry picks the model class and says
+            # which engine drives it — fixed batches over paged KV, or ragged steps (prompt chunks beside decoded tokens)
+            from ... import model_registry
+            from ...ragged_engine import RaggedStepEngine
+
+            arch, _model_cfg, shards = model_registry.load_model_dir(cfg["model_path"], device=self.device,
+                                                                    dtype=cfg.get("dtype", torch.bfloat16))
+            self.model = shards
+            if arch.engine == "ragged":
+                self.engine = RaggedStepEngine(shards, max_tokens=cfg.get("max_num_batched_tokens", 8192),
+                                               max_seqs=cfg.get("max_batch_size", 32), block_size=cfg.get("block_size", 16))
+                self.backend_type = "ragged_b200"
+                self.loaded = True
+                return
+            cfg = dict(cfg, shards=shards)
         shards = cfg.get("shards")
         if shards is None:
             model_cfg = cfg["model_config"]
@@ -140,6 +156,8 @@ class PagedLLMEngine:
         group is one equal-length batch; within a group the common leading tokens are computed once."""
         if not self.loaded:
             raise RuntimeError("model is not loaded")
+        if self.backend_type == "ragged_b200":
+            return self._batch_inference_ragged(params_list)
         results: List[Any] = [None] * len(params_list)
         groups: Dict[Any, List[int]] = {}
         parsed: Dict[int, Any] = {}
@@ -179,6 +197,21 @@ class PagedLLMEngine:
                 except Exception as exc:  # noqa: BLE001
                     for i in part:
                         results[i] = exc
+        return results
+
+    def _batch_inference_ragged(self, params_list: List[Dict[str, Any]]) -> List[Any]:
+        """Requests of any lengths through the step engine's scheduler (continuous batching, chunked prompts)."""
+        results: List[Any] = [None] * len(params_list)
+        rows, owners = [], []
+        for i, p in enumerate(params_list):
+            try:
+                ids, _n_sys = self._ids_of(p)
+                rows.append({"input_ids": ids, "max_new_tokens": int(p.get("max_tokens", p.get("max_new_tokens", 16)))})
+                owners.append(i)
+            except Exception as exc:  # noqa: BLE001
+                results[i] = exc
+        for i, row, res in zip(owners, rows, self.engine.batch_inference(rows)):
+            results[i] = res if isinstance(res, Exception) else self._result(res["output_ids"], len(row["input_ids"]), 0)
         return results
 
     # ---- LLMBaseEngine -------------------------------------------------------------------------------------------

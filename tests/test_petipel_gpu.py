@@ -620,3 +620,31 @@ def test_routed_feed_forward_16_bit_takes_the_grouped_kernel():
     loops = mod(h.to(DEV)).cpu()
     close(got, ref, 2e-2)
     close(loops, ref, 2e-2)
+
+
+def test_engine_adapter_serves_a_checkpoint_folder(tmp_path):
+    """The reference-shaped engine surface (load_model / inference / batch_inference) picks the ragged step engine
+    for a checkpoint folder whose config.json names this model class, and answers with the oracle's greedy tokens."""
+    import json
+
+    from dgi_b200 import petipel_layer as P
+    from dgi_b200.safetensors_io import write_safetensors
+    from dgi_b200.worker.engines.paged_engine import PagedLLMEngine
+
+    cfg = P.PetipelConfig.from_dict(CFG_B)
+    tensors = P.random_checkpoint(cfg, seed=7, bias_rows=9)
+    (tmp_path / "config.json").write_text(json.dumps(CFG_B))
+    write_safetensors(str(tmp_path / "model.safetensors"), tensors)
+    eng = PagedLLMEngine({"model_path": str(tmp_path), "device": DEV, "dtype": torch.float32, "max_batch_size": 2,
+                          "max_num_batched_tokens": 256})
+    eng.load_model()
+    assert eng.get_backend_info()["backend"] == "ragged_b200"
+    prompts = [tokens(n, CFG_B["vocab"], 70 + n) for n in (12, 30, 5)]
+    res = eng.batch_inference([{"input_ids": p, "max_tokens": 4} for p in prompts] + [{"nothing": 1}])
+    assert isinstance(res[3], Exception)
+    for p, r in zip(prompts, res):
+        seq = list(p)
+        for _ in range(4):
+            seq.append(int(R.forward(CFG_B, tensors, seq)[-1].argmax()))
+        assert r["output_ids"] == seq[len(p):] and r["usage"]["prompt_tokens"] == len(p)
+    eng.unload_model()
