@@ -58,8 +58,8 @@ def test_checkpoint_container_round_trip(tmp_path):
 
 
 def test_bucket_rule():
-    assert [P.log_distance_bucket(n, 32, 240) for n in (0, 1, 15, 16, 17, 239, 240, 5000)] == \
-        [0, 1, 15, 16, 16, 31, 31, 31]
+    assert [P.log_distance_bucket(n, 24, 100) for n in (0, 1, 11, 12, 13, 99, 100, 5000)] == \
+        [0, 1, 11, 12, 12, 23, 23, 23]
     for rows, far in ((12, 40), (7, 20.5), (9, 64)):
         last = -1
         for n in range(0, 200):
