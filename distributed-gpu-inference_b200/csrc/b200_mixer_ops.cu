@@ -858,9 +858,9 @@ gated_scan_kernel(float* __restrict__ o_raw, const T* __restrict__ zq, const T* 
 // rows i = r, r + 4, ... of that column in REGISTERS for the whole portion.  A token costs dk / 4 state updates per
 // thread, two shuffles to add the four partial read-outs, and no barrier; q and f of a token are broadcast reads
 // from shared memory, stored there grouped by r.  The CTA (128 threads = 32 columns) stages the activated inputs of
-// 16 tokens at a time, double buffered: raw loads of the next 16 tokens are issued before the current 16 are
-// computed and converted afterwards, one barrier per 16 tokens.  The summation order of a read-out is fixed by dk.
-constexpr int kScanChunk = 16;
+// 4 tokens at a time, double buffered: raw loads of the next 4 tokens are issued before the current 4 are
+// computed and converted afterwards, one barrier per 4 tokens.  The summation order of a read-out is fixed by dk.
+constexpr int kScanChunk = 4;
 constexpr int kScanNT = 128;
 constexpr int kScanColsR = kScanNT / 4;   // value columns per CTA
 
@@ -1338,7 +1338,9 @@ int b200_gated_scan(float* o_raw, const void* zq, const void* zf, const void* v,
   if (dk <= 128 && max_count >= 8) {
     // register kernel: 32 value columns per CTA, four lanes per column
     const int dkt = dk <= 16 ? 16 : (dk <= 32 ? 32 : (dk <= 64 ? 64 : 128));
-    const size_t smem_c = sizeof(float) * 2 * kScanChunk * (2 * static_cast<size_t>(dkt) + kScanColsR);
+    // the staging buffers double as the [dk][32] slab the state moves through at both ends of the kernel
+    const size_t smem_c = sizeof(float) * std::max<size_t>(2 * kScanChunk * (2 * static_cast<size_t>(dkt) + kScanColsR),
+                                                           static_cast<size_t>(dkt) * kScanColsR);
     const dim3 grid_c(n_seqs, H, (dv + kScanColsR - 1) / kScanColsR);
     return mixer_by_dtype(dtype, "b200_gated_scan", [&](auto* tag) {
       using T = std::remove_pointer_t<decltype(tag)>;
