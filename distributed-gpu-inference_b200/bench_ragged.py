@@ -4,7 +4,7 @@ of every mixer kernel of one prompt step and one decode step against its memory 
 
 Random weights, synthetic token ids; bf16.  Timed with CUDA events on the launching stream after warm-up; the
 inputs of a step (activations, weights, KV of all sequences) exceed L2 at the two larger sizes and the report says
-so per size.  One JSON line on stdout; the default workload and contract of bench.py are untouched.
+so per size.  One JSON line on stdout; the default workload and output line of bench.py are untouched.
 """
 from __future__ import annotations
 

@@ -258,7 +258,7 @@ biased_paged_attn_kernel(T* __restrict__ out, const T* __restrict__ q, int64_t q
   if constexpr (NCH > 0) prefetch(0);
 
   for (int j0 = 0; j0 <= pos_last; j0 += kKeyTile) {
-    __syncthreads();  // previous tile fully consumed (and q_s written, first time round)
+    __syncthreads();  // previous tile fully consumed (and q_s written, on the first pass)
     const int n_keys = min(kKeyTile, pos_last + 1 - j0);
     if constexpr (NCH > 0) {
       commit();
