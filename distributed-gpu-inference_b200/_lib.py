@@ -128,6 +128,30 @@ MIXER_SIGNATURES = {
     "b200_grouped_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_clamped_glu": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_float, c_float, c_int, c_void_p]),
     "b200_expert_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    # pieces for hybrid designs (csrc/b200_hybrid_ops.cu)
+    "b200_rms_norm": (c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_float, c_float, c_int, c_int, c_int,
+                              c_void_p]),
+    "b200_residual_add2_norm": (
+        c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_float, c_int, c_int, c_int,
+                c_void_p]),
+    "b200_xielu": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_rotary_kv_append": (
+        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int64, c_int, c_void_p]),
+    "b200_norm_append": (
+        c_int, [c_void_p, c_int64, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_mixed_paged_attn": (
+        c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_float, c_int,
+                c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_causal_conv_silu": (
+        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                c_void_p]),
+    "b200_delta_scan": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p,
+                c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
+    "b200_head_rmsnorm_gated": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_int64, c_int, c_int, c_int, c_void_p]),
 }
 
 _lock = threading.Lock()
@@ -183,7 +207,7 @@ def _build_mixers() -> None:
         fcntl.flock(lock, fcntl.LOCK_EX)
         if os.path.exists(MIXER_LIB_PATH):
             return
-        proc = subprocess.run(["make", "-C", csrc, "mixers"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        proc = subprocess.run(["make", "-j2", "-C", csrc, "mixers"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
         if proc.returncode != 0 or not os.path.exists(MIXER_LIB_PATH):
             raise B200LibraryError("building libb200_mixers.so failed:\n" + proc.stdout.decode(errors="replace")[-4000:])
 

@@ -1,0 +1,827 @@
+// Mixers and feed-forward pieces for hybrid decoder designs whose layers read ONE norm of an fp32 residual stream and
+// add the mixer's and the feed-forward's outputs to it together:
+//
+//   RMS norm                    y = x * rsqrt(mean(x^2) + eps) * (offset + w), fp32 or storage-dtype rows in, strided
+//   two-branch residual update  x += (a + b), optionally followed by the next layer's input norm
+//   xIELU activation            z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (e^z - 1 - z) + z/2
+//   rotary K/V append           partial rotary on q and k, optional rotation of the VALUES over their whole width,
+//                               k and v scattered into the paged pools; angles are formed in double precision
+//   norm + latent append        RMS-normed latent rows scattered into a one-head pool (keys and values of a latent
+//                               attention are the same cached rows)
+//   mixed-head paged attention  softmax attention of packed query rows over the paged cache with (all optional) a
+//                               sliding window that keeps the first tokens of the sequence, a learned sink logit in
+//                               the denominator, a head-mixing matrix applied to the scores before the softmax, the
+//                               inverse value rotation of the output and a per-head sigmoid gate
+//   short causal convolution    per channel over a sequence's tokens, then SiLU; the last taps - 1 inputs of every
+//                               live sequence are carried in a slot pool
+//   gated delta rule            S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q  with a decay per
+//                               key channel, the fp32 state carried per sequence in a slot pool
+//   gated head norm             o * rsqrt(mean(o^2) + eps) * w * sigmoid(gate)
+//
+// Every size and constant of a design is a parameter.  Scores, softmax, norms, decays, the state and the residual
+// are fp32 whatever the storage dtype T is.  The order in which a position's sums are formed depends only on that
+// position and the layer's sizes, never on how a batch was cut or what else is in it.
+#include <algorithm>
+#include <type_traits>
+
+#include "../../include/b200_mixers.h"
+#include "b200_common.cuh"
+
+namespace b200 {
+namespace {
+
+template <typename F>
+int hybrid_by_dtype(int dtype, const char* name, F&& f) {
+  switch (dtype) {
+    case B200_DTYPE_F16:
+      return f(static_cast<__half*>(nullptr));
+    case B200_DTYPE_BF16:
+      return f(static_cast<__nv_bfloat16*>(nullptr));
+    case B200_DTYPE_F32:
+      return f(static_cast<float*>(nullptr));
+    default:
+      return fail(B200_EINVAL, "%s: unsupported dtype %d", name, dtype);
+  }
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  // every thread returns the total; `red` holds 32 floats and may be reused after the call's second barrier
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+
+__device__ __forceinline__ float sigmoid_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
+
+// ---- RMS norm ----------------------------------------------------------------------------------------------------
+template <typename T, typename X>
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(T* __restrict__ out, int64_t out_stride, const X* __restrict__ x, int64_t x_stride,
+                const T* __restrict__ w, float w_off, float eps, int width) {
+  __shared__ float red[32];
+  const X* xr = x + static_cast<int64_t>(blockIdx.x) * x_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = Cvt<X>::to_f32(xr[i]);
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / static_cast<float>(width) + eps);
+  T* orow = out + static_cast<int64_t>(blockIdx.x) * out_stride;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    orow[i] = Cvt<T>::from_f32(Cvt<X>::to_f32(xr[i]) * inv * (w_off + Cvt<T>::to_f32(w[i])));
+}
+
+// ---- x += (a + b); optionally out_next = norm(x; w_next) ---------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+residual_add2_norm_kernel(float* __restrict__ x, const T* __restrict__ a, int64_t a_stride, const T* __restrict__ b,
+                          int64_t b_stride, const T* __restrict__ w_next, float w_off, T* __restrict__ out_next,
+                          float eps, int width) {
+  extern __shared__ float row_s[];
+  __shared__ float red[32];
+  float* xr = x + static_cast<int64_t>(blockIdx.x) * width;
+  const T* ar = a + static_cast<int64_t>(blockIdx.x) * a_stride;
+  const T* br = b ? b + static_cast<int64_t>(blockIdx.x) * b_stride : nullptr;
+  float sx = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float y = Cvt<T>::to_f32(ar[i]);
+    if (br) y += Cvt<T>::to_f32(br[i]);
+    const float v = xr[i] + y;
+    xr[i] = v;
+    row_s[i] = v;
+    sx = fmaf(v, v, sx);
+  }
+  if (w_next == nullptr) return;
+  const float inv = rsqrtf(block_sum(sx, red) / static_cast<float>(width) + eps);
+  T* orow = out_next + static_cast<int64_t>(blockIdx.x) * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    orow[i] = Cvt<T>::from_f32(row_s[i] * inv * (w_off + Cvt<T>::to_f32(w_next[i])));
+}
+
+// ---- xIELU -------------------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+xielu_kernel(T* __restrict__ out, const T* __restrict__ z, int64_t z_stride, const T* __restrict__ pq, int ff,
+             int64_t total) {
+  const float ap = softplus_(Cvt<T>::to_f32(pq[0]));
+  const float an = 0.5f + softplus_(Cvt<T>::to_f32(pq[1]));
+  for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+       e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = e / ff;
+    const int c = static_cast<int>(e - r * ff);
+    const float v = Cvt<T>::to_f32(z[r * z_stride + c]);
+    const float y = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
+    out[e] = Cvt<T>::from_f32(y);
+  }
+}
+
+// ---- rotary K/V append ---------------------------------------------------------------------------------------------
+// One CTA per token.  The token's cos / sin tables (rot_dims / 2 entries for q and k, dv / 2 for the values) are
+// formed in double precision from the integer position, so a position of any size keeps full fp32 accuracy.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rotary_kv_append_kernel(T* __restrict__ q, int64_t q_stride, const T* __restrict__ k, int64_t k_stride,
+                        const T* __restrict__ v, int64_t v_stride, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                        const int64_t* __restrict__ slot_mapping, const int32_t* __restrict__ tok_pos, int H, int G, int dk,
+                        int dv, int rot_dims, double rot_base, int rotate_values, int interleaved, int block_size) {
+  extern __shared__ float tab[];   // cos_qk[rh] sin_qk[rh] cos_v[vh] sin_v[vh]
+  const int n = blockIdx.x;
+  const int rh = rot_dims / 2, vh = rotate_values ? dv / 2 : 0;
+  float* cq = tab;
+  float* sq = cq + rh;
+  float* cv = sq + rh;
+  float* sv = cv + vh;
+  const double p = static_cast<double>(tok_pos[n]);
+  for (int i = threadIdx.x; i < rh + vh; i += blockDim.x) {
+    const bool is_v = i >= rh;
+    const int m = is_v ? i - rh : i;
+    const double a = p * pow(rot_base, -2.0 * m / static_cast<double>(is_v ? dv : rot_dims));
+    double s, c;
+    sincos(a, &s, &c);
+    if (is_v) { cv[m] = static_cast<float>(c); sv[m] = static_cast<float>(s); }
+    else { cq[m] = static_cast<float>(c); sq[m] = static_cast<float>(s); }
+  }
+  __syncthreads();
+  const int64_t slot = slot_mapping[n];
+  const int64_t blk = slot >= 0 ? slot / block_size : 0;
+  const int off = slot >= 0 ? static_cast<int>(slot - blk * block_size) : 0;
+  // q: in place.  a work item is one pair (or one unrotated element, counted past the pairs)
+  {
+    T* qr = q + static_cast<int64_t>(n) * q_stride;
+    const int per = rh + (dk - rot_dims);
+    for (int e = threadIdx.x; e < H * per; e += blockDim.x) {
+      const int h = e / per, i = e - h * per;
+      if (i >= rh) continue;                          // elements past the rotated part stay as they are
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + rh;
+      const float u = Cvt<T>::to_f32(qr[h * dk + a]), w = Cvt<T>::to_f32(qr[h * dk + b]);
+      qr[h * dk + a] = Cvt<T>::from_f32(u * cq[i] - w * sq[i]);
+      qr[h * dk + b] = Cvt<T>::from_f32(w * cq[i] + u * sq[i]);
+    }
+  }
+  if (slot < 0) return;
+  {
+    const T* kr = k + static_cast<int64_t>(n) * k_stride;
+    const int per = rh + (dk - rot_dims);
+    for (int e = threadIdx.x; e < G * per; e += blockDim.x) {
+      const int g = e / per, i = e - g * per;
+      T* dst = k_pool + ((blk * G + g) * block_size + off) * dk;
+      if (i >= rh) {
+        dst[rot_dims + i - rh] = kr[g * dk + rot_dims + i - rh];
+        continue;
+      }
+      const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + rh;
+      const float u = Cvt<T>::to_f32(kr[g * dk + a]), w = Cvt<T>::to_f32(kr[g * dk + b]);
+      dst[a] = Cvt<T>::from_f32(u * cq[i] - w * sq[i]);
+      dst[b] = Cvt<T>::from_f32(w * cq[i] + u * sq[i]);
+    }
+  }
+  {
+    const T* vr = v + static_cast<int64_t>(n) * v_stride;
+    if (rotate_values) {
+      for (int e = threadIdx.x; e < G * vh; e += blockDim.x) {
+        const int g = e / vh, i = e - g * vh;
+        T* dst = v_pool + ((blk * G + g) * block_size + off) * dv;
+        const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + vh;
+        const float u = Cvt<T>::to_f32(vr[g * dv + a]), w = Cvt<T>::to_f32(vr[g * dv + b]);
+        dst[a] = Cvt<T>::from_f32(u * cv[i] - w * sv[i]);
+        dst[b] = Cvt<T>::from_f32(w * cv[i] + u * sv[i]);
+      }
+      if (dv & 1)   // an odd last element has no partner
+        for (int g = threadIdx.x; g < G; g += blockDim.x)
+          v_pool[((blk * G + g) * block_size + off) * dv + dv - 1] = vr[g * dv + dv - 1];
+    } else {
+      for (int e = threadIdx.x; e < G * dv; e += blockDim.x) {
+        const int g = e / dv, i = e - g * dv;
+        v_pool[((blk * G + g) * block_size + off) * dv + i] = vr[e];
+      }
+    }
+  }
+}
+
+// ---- RMS norm + append of a latent row ---------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(128)
+norm_append_kernel(const T* __restrict__ x, int64_t x_stride, const T* __restrict__ w, float w_off, float eps,
+                   T* __restrict__ pool, const int64_t* __restrict__ slot_mapping, int width) {
+  __shared__ float red[32];
+  const T* xr = x + static_cast<int64_t>(blockIdx.x) * x_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = Cvt<T>::to_f32(xr[i]);
+    ss = fmaf(v, v, ss);
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / static_cast<float>(width) + eps);
+  const int64_t slot = slot_mapping[blockIdx.x];
+  if (slot < 0) return;
+  T* dst = pool + slot * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    dst[i] = Cvt<T>::from_f32(Cvt<T>::to_f32(xr[i]) * inv * (w_off + Cvt<T>::to_f32(w[i])));
+}
+
+// ---- mixed-head paged attention (row form) -------------------------------------------------------------------------
+// One CTA per (token, pass of HP heads), four warps.  The keys a position sees are cut into chunks of 32 at absolute
+// multiples of 32; the chunks a window skips are never visited.  Warp w takes visible chunks w, w + 4, ... with one key
+// per lane for the scores (all heads when a mixing matrix couples them) and one value channel per lane for P.V, keeps a
+// running (max, sum, output) per head, and the four partial results are merged through shared memory.  The sink
+// logit enters the denominator in the merge.
+struct AttnArgs {
+  void* out; int64_t out_tok_stride, out_head_stride;
+  const void* q; int64_t q_tok_stride, q_head_stride;
+  const void* gate; int64_t gate_stride;
+  const void* k_pool; const void* v_pool;
+  const int32_t* block_tables; int table_stride;
+  const int32_t* tok_row; const int32_t* tok_pos;
+  const float* talk; const float* sink;
+  float scale; int window, keep_first, unrotate, interleaved; double rot_base;
+  int H, G, dk, dv, block_size;
+};
+
+constexpr int kAttnWarpsRow = 4;
+
+template <typename T>
+__device__ __forceinline__ float dot_row(const float* __restrict__ qs, const T* __restrict__ kr, int dk, bool vec) {
+  float s = 0.f;
+  if (vec) {
+    constexpr int E = 16 / sizeof(T);
+    for (int d = 0; d < dk; d += E) {
+      const int4 raw = *reinterpret_cast<const int4*>(kr + d);
+      const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int u = 0; u < E; ++u) s = fmaf(qs[d + u], Cvt<T>::to_f32(e[u]), s);
+    }
+  } else {
+    for (int d = 0; d < dk; ++d) s = fmaf(qs[d], Cvt<T>::to_f32(kr[d]), s);
+  }
+  return s;
+}
+
+template <typename T, int HP, int DVC>
+__global__ void __launch_bounds__(kAttnWarpsRow * 32)
+mixed_paged_attn_kernel(const AttnArgs A) {
+  extern __shared__ __align__(16) float sm[];
+  const int n = blockIdx.x, h0 = blockIdx.y * HP;
+  const int H = A.H, G = A.G, dk = A.dk, dv = A.dv, bs = A.block_size, rep = H / G;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool mixed = A.talk != nullptr;
+  const int hs0 = mixed ? 0 : h0;                         // first head whose raw scores are formed here
+  const int nhs = mixed ? H : min(HP, H - h0);            // and how many
+  float* q_s = sm;                                        // [nhs][dk]
+  float* raw_s = q_s + nhs * dk;                          // [warps][nhs][32]
+  float* talk_s = raw_s + kAttnWarpsRow * nhs * 32;       // [HP][H]
+  float* mrg = talk_s + (mixed ? HP * H : 0);             // [warps][HP][dv + 2], later [HP][dv] of results
+  const T* q = static_cast<const T*>(A.q) + static_cast<int64_t>(n) * A.q_tok_stride;
+  for (int e = threadIdx.x; e < nhs * dk; e += blockDim.x) {
+    const int hh = e / dk, d = e - hh * dk;
+    q_s[e] = Cvt<T>::to_f32(q[(hs0 + hh) * A.q_head_stride + d]) * A.scale;
+  }
+  if (mixed)
+    for (int e = threadIdx.x; e < HP * H; e += blockDim.x) {
+      const int hl = e / H;
+      talk_s[e] = (h0 + hl < H) ? A.talk[(h0 + hl) * H + (e - hl * H)] : 0.f;
+    }
+  __syncthreads();
+  const int p = A.tok_pos[n];
+  const int32_t* table = A.block_tables + static_cast<int64_t>(A.tok_row[n]) * A.table_stride;
+  const int lo = A.window > 0 ? max(0, p - A.window + 1) : 0;
+  const int kf = A.window > 0 ? min(A.keep_first, lo) : 0;   // kept first tokens that the window no longer covers
+  const int nA = (kf + 31) >> 5;
+  const int cB0 = max(nA, lo >> 5), cB1 = p >> 5;
+  const int n_chunks = nA + (cB1 - cB0 + 1);
+  const T* kp = static_cast<const T*>(A.k_pool);
+  const T* vp = static_cast<const T*>(A.v_pool);
+  const bool vec = (dk * sizeof(T)) % 16 == 0;
+  float m_r[HP], l_r[HP], acc[HP][DVC];
+#pragma unroll
+  for (int hl = 0; hl < HP; ++hl) {
+    m_r[hl] = -INFINITY;
+    l_r[hl] = 0.f;
+#pragma unroll
+    for (int cc = 0; cc < DVC; ++cc) acc[hl][cc] = 0.f;
+  }
+  float* raw_w = raw_s + warp * nhs * 32;
+  for (int idx = warp; idx < n_chunks; idx += kAttnWarpsRow) {
+    const int c = idx < nA ? idx : cB0 + idx - nA;
+    const int j = c * 32 + lane;
+    const bool valid = j <= p && (A.window <= 0 || p - j < A.window || j < A.keep_first);
+    int base = 0;                                            // row of the key in head 0 of its block
+    if (valid) base = (table[j / bs] * G) * bs + j % bs;
+    __syncwarp();
+    if (valid) {
+      for (int hh = 0; hh < nhs; ++hh) {
+        const int g = (hs0 + hh) / rep;
+        raw_w[hh * 32 + lane] = dot_row<T>(q_s + hh * dk, kp + static_cast<int64_t>(base + g * bs) * dk, dk, vec);
+      }
+    }
+    __syncwarp();
+    float pr[HP];
+#pragma unroll
+    for (int hl = 0; hl < HP; ++hl) {
+      pr[hl] = 0.f;
+      if (h0 + hl < H) {          // uniform over the warp
+        float t = -INFINITY;
+        if (valid) {
+          if (mixed) {
+            t = 0.f;
+            for (int g = 0; g < H; ++g) t = fmaf(talk_s[hl * H + g], raw_w[g * 32 + lane], t);
+          } else {
+            t = raw_w[hl * 32 + lane];
+          }
+        }
+        const float m_new = fmaxf(m_r[hl], warp_max(t));
+        if (m_new != -INFINITY) {
+          const float corr = expf(m_r[hl] - m_new);          // exp(-inf) = 0 for the first chunk with a visible key
+          const float e = valid ? expf(t - m_new) : 0.f;
+          l_r[hl] = l_r[hl] * corr + warp_sum(e);
+          m_r[hl] = m_new;
+          pr[hl] = e;
+#pragma unroll
+          for (int cc = 0; cc < DVC; ++cc) acc[hl][cc] *= corr;
+        }
+      }
+    }
+    for (int jj = 0; jj < 32; ++jj) {
+      const int vbase = __shfl_sync(0xffffffffu, base, jj);
+      float vv[DVC];
+      int g_have = -1;
+#pragma unroll
+      for (int hl = 0; hl < HP; ++hl) {
+        const float pj = __shfl_sync(0xffffffffu, pr[hl], jj);
+        if (pj != 0.f) {         // uniform over the warp; also skips heads past H and keys that are masked
+          const int g = (h0 + hl) / rep;
+          if (g != g_have) {
+            const T* vr = vp + static_cast<int64_t>(vbase + g * bs) * dv;
+#pragma unroll
+            for (int cc = 0; cc < DVC; ++cc) vv[cc] = (lane + 32 * cc < dv) ? Cvt<T>::to_f32(vr[lane + 32 * cc]) : 0.f;
+            g_have = g;
+          }
+#pragma unroll
+          for (int cc = 0; cc < DVC; ++cc) acc[hl][cc] = fmaf(pj, vv[cc], acc[hl][cc]);
+        }
+      }
+    }
+  }
+  // merge the warps' partial results
+  const int mw = dv + 2;
+#pragma unroll
+  for (int hl = 0; hl < HP; ++hl) {
+    float* dst = mrg + (warp * HP + hl) * mw;
+#pragma unroll
+    for (int cc = 0; cc < DVC; ++cc)
+      if (lane + 32 * cc < dv) dst[lane + 32 * cc] = acc[hl][cc];
+    if (lane == 0) { dst[dv] = m_r[hl]; dst[dv + 1] = l_r[hl]; }
+  }
+  __syncthreads();
+  float* res = raw_s;    // [HP][dv] — the score staging area is free now (nhs * 128 >= HP * dv is checked on the host)
+  for (int e = threadIdx.x; e < HP * dv; e += blockDim.x) {
+    const int hl = e / dv, c = e - hl * dv;
+    if (h0 + hl >= H) continue;
+    float M = A.sink ? A.sink[h0 + hl] : -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarpsRow; ++w) M = fmaxf(M, mrg[(w * HP + hl) * mw + dv]);
+    float L = A.sink ? expf(A.sink[h0 + hl] - M) : 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarpsRow; ++w) {
+      const float* src = mrg + (w * HP + hl) * mw;
+      const float f = src[dv] == -INFINITY ? 0.f : expf(src[dv] - M);
+      L = fmaf(src[dv + 1], f, L);
+      O = fmaf(src[c], f, O);
+    }
+    res[e] = O / L;
+  }
+  __syncthreads();
+  T* out = static_cast<T*>(A.out) + static_cast<int64_t>(n) * A.out_tok_stride;
+  const T* gate = static_cast<const T*>(A.gate);
+  if (A.unrotate) {
+    const int vh = dv / 2;
+    for (int e = threadIdx.x; e < HP * vh; e += blockDim.x) {
+      const int hl = e / vh, i = e - hl * vh;
+      if (h0 + hl >= H) continue;
+      double s, c;
+      sincos(static_cast<double>(p) * pow(A.rot_base, -2.0 * i / static_cast<double>(dv)), &s, &c);
+      const float cf = static_cast<float>(c), sf = static_cast<float>(s);
+      const int a = A.interleaved ? 2 * i : i, b = A.interleaved ? 2 * i + 1 : i + vh;
+      const float u = res[hl * dv + a], w = res[hl * dv + b];
+      float ya = u * cf + w * sf, yb = w * cf - u * sf;        // the rotation by -p
+      if (gate) {
+        const float gt = sigmoid_(Cvt<T>::to_f32(gate[static_cast<int64_t>(n) * A.gate_stride + h0 + hl]));
+        ya *= gt; yb *= gt;
+      }
+      T* orow = out + (h0 + hl) * A.out_head_stride;
+      orow[a] = Cvt<T>::from_f32(ya);
+      orow[b] = Cvt<T>::from_f32(yb);
+    }
+    if (dv & 1)
+      for (int hl = threadIdx.x; hl < HP; hl += blockDim.x)
+        if (h0 + hl < H) out[(h0 + hl) * A.out_head_stride + dv - 1] = Cvt<T>::from_f32(res[hl * dv + dv - 1]);
+  } else {
+    for (int e = threadIdx.x; e < HP * dv; e += blockDim.x) {
+      const int hl = e / dv, c = e - hl * dv;
+      if (h0 + hl >= H) continue;
+      float y = res[e];
+      if (gate) y *= sigmoid_(Cvt<T>::to_f32(gate[static_cast<int64_t>(n) * A.gate_stride + h0 + hl]));
+      out[(h0 + hl) * A.out_head_stride + c] = Cvt<T>::from_f32(y);
+    }
+  }
+}
+
+// ---- short causal convolution + SiLU -----------------------------------------------------------------------------
+struct SeqSpan {
+  int tok0;   // first packed row
+  int count;  // tokens in this step
+  int slot;   // state slot
+  int fresh;  // 1: the sequence starts here (state is zero)
+};
+
+constexpr int kConvTokens = 64;   // tokens per CTA; at least taps - 1, so only a sequence's first CTA reads the carried inputs
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+causal_conv_silu_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ x, int64_t x_stride,
+                        const T* __restrict__ w, float* __restrict__ tail, const SeqSpan* __restrict__ seqs, int C,
+                        int taps) {
+  const SeqSpan sq = seqs[blockIdx.x];
+  const int t0 = blockIdx.y * kConvTokens;
+  if (t0 >= sq.count) return;
+  const int c = blockIdx.z * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  constexpr int kMaxTaps = 8;
+  float wr[kMaxTaps], old[kMaxTaps];
+#pragma unroll
+  for (int i = 0; i < kMaxTaps; ++i) {
+    wr[i] = i < taps ? Cvt<T>::to_f32(w[static_cast<int64_t>(c) * taps + i]) : 0.f;
+    old[i] = 0.f;
+  }
+  float* tl = tail + static_cast<int64_t>(sq.slot) * (taps - 1) * C + c;   // [taps - 1][C], oldest first
+  if (t0 == 0 && !sq.fresh)
+#pragma unroll
+    for (int i = 0; i < kMaxTaps - 1; ++i)
+      if (i < taps - 1) old[i] = tl[static_cast<int64_t>(i) * C];
+  const T* xc = x + static_cast<int64_t>(sq.tok0) * x_stride + c;
+  auto input = [&](int t) -> float {    // the channel's input at step t of this portion; t < 0 reaches into the carry
+    if (t >= 0) return Cvt<T>::to_f32(xc[static_cast<int64_t>(t) * x_stride]);
+    float r = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxTaps - 1; ++i)
+      if (i == taps - 1 + t) r = old[i];
+    return r;
+  };
+  const int t1 = min(sq.count, t0 + kConvTokens);
+  for (int t = t0; t < t1; ++t) {
+    float y = 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxTaps; ++i)
+      if (i < taps) y = fmaf(wr[i], input(t - (taps - 1 - i)), y);
+    out[static_cast<int64_t>(sq.tok0 + t) * out_stride + c] = Cvt<T>::from_f32(y * sigmoid_(y));
+  }
+  if (t0 == 0) {
+    // the new carry: the portion's last taps - 1 inputs (older ones come from the old carry when the portion is short)
+    float nw[kMaxTaps];
+#pragma unroll
+    for (int i = 0; i < kMaxTaps - 1; ++i) nw[i] = (i < taps - 1) ? input(sq.count - (taps - 1) + i) : 0.f;
+#pragma unroll
+    for (int i = 0; i < kMaxTaps - 1; ++i)
+      if (i < taps - 1) tl[static_cast<int64_t>(i) * C] = nw[i];
+  }
+}
+
+// ---- gated delta rule --------------------------------------------------------------------------------------------
+// One CTA per (sequence, head, 32 value columns): a value column's part of the state never meets another column's, so
+// columns are independent.  Four adjacent lanes share a column; lane r keeps the state rows i = r, r + 4, ... of that
+// column in registers for the whole portion.  Four tokens are staged at a time: their activated q and k (unit length
+// per head, q also scaled), the decays g = exp(-exp(A_log) softplus(a + dt_bias)), the write strength sigmoid(b) and
+// the CTA's value columns.  Per token: S <- g S and d = S^T k in one pass, u = beta (v - d), then S <- S + k u and
+// o = S^T q in a second pass; the four lanes' partial sums meet in two shuffles.
+constexpr int kDeltaChunk = 4;
+constexpr int kDeltaNT = 128;
+constexpr int kDeltaCols = kDeltaNT / 4;
+
+struct DeltaArgs {
+  float* o_raw;
+  const void* q; const void* k; const void* v; int64_t in_stride;
+  const void* beta; int64_t beta_stride;
+  const void* a; int64_t a_stride;
+  const void* dt_bias; const void* a_log;
+  float* state; const SeqSpan* seqs;
+  int H, G, dk, dv; float unit_eps, q_scale;
+};
+
+template <typename T, int DK>
+__global__ void __launch_bounds__(kDeltaNT)
+delta_scan_kernel(const DeltaArgs A) {
+  extern __shared__ __align__(16) float smem[];
+  constexpr int RW4 = DK / 4;
+  constexpr int row_len = 3 * DK + kDeltaCols + 4;      // q | k | g (each grouped by r) | v[32] | beta, pad
+  const SeqSpan sq = A.seqs[blockIdx.x];
+  const int h = blockIdx.y, H = A.H, dk = A.dk, dv = A.dv;
+  const int gq = h / (H / A.G);                          // the q / k head this value head reads
+  const int r = threadIdx.x & 3, cl = threadIdx.x >> 2;
+  const int col0 = blockIdx.z * kDeltaCols, col = col0 + cl;
+  const int ncol = min(kDeltaCols, dv - col0);
+  const bool has_col = col < dv;
+  float* st = A.state + (static_cast<int64_t>(sq.slot) * H + h) * dk * dv;
+  float S[RW4];
+#pragma unroll
+  for (int kk = 0; kk < RW4; ++kk) {
+    const int i = 4 * kk + r;
+    S[kk] = (!sq.fresh && i < dk && has_col) ? st[static_cast<int64_t>(i) * dv + col] : 0.f;
+  }
+  const T* qp = static_cast<const T*>(A.q);
+  const T* kp = static_cast<const T*>(A.k);
+  const T* vp = static_cast<const T*>(A.v);
+  const T* bp = static_cast<const T*>(A.beta);
+  const T* ap = static_cast<const T*>(A.a);
+  const T* dtb = static_cast<const T*>(A.dt_bias);
+  const float a_rate = expf(Cvt<T>::to_f32(static_cast<const T*>(A.a_log)[h]));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int t0 = 0; t0 < sq.count; t0 += kDeltaChunk) {
+    const int n_here = min(kDeltaChunk, sq.count - t0);
+    __syncthreads();          // the previous chunk has been consumed
+    for (int e = threadIdx.x; e < n_here * row_len; e += kDeltaNT) {
+      const int tt = e / row_len, sl = e - tt * row_len;
+      const int64_t tok = sq.tok0 + t0 + tt;
+      float val = 0.f;
+      if (sl < 3 * DK) {
+        const int which = sl / DK, s2 = sl - which * DK;
+        const int i = 4 * (s2 % RW4) + s2 / RW4;         // slot r * RW4 + kk holds row 4 kk + r
+        if (i < dk) {
+          if (which == 0) val = Cvt<T>::to_f32(qp[tok * A.in_stride + gq * dk + i]);
+          else if (which == 1) val = Cvt<T>::to_f32(kp[tok * A.in_stride + gq * dk + i]);
+          else
+            val = expf(-a_rate * softplus_(Cvt<T>::to_f32(ap[tok * A.a_stride + h * dk + i]) +
+                                           Cvt<T>::to_f32(dtb[h * dk + i])));
+        }
+      } else if (sl < 3 * DK + kDeltaCols) {
+        const int c = sl - 3 * DK;
+        if (c < ncol) val = Cvt<T>::to_f32(vp[tok * A.in_stride + h * dv + col0 + c]);
+      } else if (sl == 3 * DK + kDeltaCols) {
+        val = sigmoid_(Cvt<T>::to_f32(bp[tok * A.beta_stride + h]));
+      }
+      smem[e] = val;
+    }
+    __syncthreads();
+    if (warp < n_here) {      // warp w brings token w's q and k to unit length
+      float* row = smem + warp * row_len;
+      float sq2 = 0.f, sk2 = 0.f;
+      for (int i = lane; i < DK; i += 32) {
+        sq2 = fmaf(row[i], row[i], sq2);
+        sk2 = fmaf(row[DK + i], row[DK + i], sk2);
+      }
+      const float iq = rsqrtf(warp_sum(sq2) + A.unit_eps) * A.q_scale;
+      const float ik = rsqrtf(warp_sum(sk2) + A.unit_eps);
+      for (int i = lane; i < DK; i += 32) {
+        row[i] *= iq;
+        row[DK + i] *= ik;
+      }
+    }
+    __syncthreads();
+    for (int tt = 0; tt < n_here; ++tt) {
+      const float* row = smem + tt * row_len;
+      const float* qr = row + r * RW4;
+      const float* kr = row + DK + r * RW4;
+      const float* gr = row + 2 * DK + r * RW4;
+      const float vc = row[3 * DK + cl], beta = row[3 * DK + kDeltaCols];
+      float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < RW4; kk += 2) {
+        S[kk] *= gr[kk];
+        d0 = fmaf(S[kk], kr[kk], d0);
+        S[kk + 1] *= gr[kk + 1];
+        d1 = fmaf(S[kk + 1], kr[kk + 1], d1);
+      }
+      float d = d0 + d1;
+      d += __shfl_xor_sync(0xffffffffu, d, 1);
+      d += __shfl_xor_sync(0xffffffffu, d, 2);
+      const float u = beta * (vc - d);
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int kk = 0; kk < RW4; kk += 2) {
+        S[kk] = fmaf(kr[kk], u, S[kk]);
+        o0 = fmaf(S[kk], qr[kk], o0);
+        S[kk + 1] = fmaf(kr[kk + 1], u, S[kk + 1]);
+        o1 = fmaf(S[kk + 1], qr[kk + 1], o1);
+      }
+      float o = o0 + o1;
+      o += __shfl_xor_sync(0xffffffffu, o, 1);
+      o += __shfl_xor_sync(0xffffffffu, o, 2);
+      if (r == 0 && has_col) A.o_raw[(static_cast<int64_t>(sq.tok0 + t0 + tt) * H + h) * dv + col] = o;
+    }
+  }
+#pragma unroll
+  for (int kk = 0; kk < RW4; ++kk) {
+    const int i = 4 * kk + r;
+    if (i < dk && has_col) st[static_cast<int64_t>(i) * dv + col] = S[kk];
+  }
+}
+
+// ---- o * rsqrt(mean(o^2) + eps) * w * sigmoid(gate); one warp per (token, head) ------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+head_rmsnorm_gated_kernel(T* __restrict__ out, const float* __restrict__ x, const T* __restrict__ w,
+                          const T* __restrict__ gate, int64_t gate_stride, float eps, int64_t rows, int H, int dv) {
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float* xr = x + row * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) ss = fmaf(xr[i], xr[i], ss);
+  const float inv = rsqrtf(warp_sum(ss) / static_cast<float>(dv) + eps);
+  const int64_t n = row / H;
+  const int h = static_cast<int>(row - n * H);
+  const T* gr = gate ? gate + n * gate_stride + static_cast<int64_t>(h) * dv : nullptr;
+  for (int i = lane; i < dv; i += 32) {
+    float y = xr[i] * inv * Cvt<T>::to_f32(w[i]);
+    if (gr) y *= sigmoid_(Cvt<T>::to_f32(gr[i]));
+    out[row * dv + i] = Cvt<T>::from_f32(y);
+  }
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int b200_rms_norm(void* out, int64_t out_stride, const void* x, int64_t x_stride, int x_is_f32, const void* weight,
+                  float weight_offset, float eps, int rows, int width, int dtype, void* stream) {
+  if (rows < 0 || width <= 0) return fail(B200_EINVAL, "b200_rms_norm: bad sizes");
+  if (rows == 0) return 0;
+  if (!out || !x || !weight) return fail(B200_EINVAL, "b200_rms_norm: null pointer");
+  return hybrid_by_dtype(dtype, "b200_rms_norm", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (x_is_f32)
+      rms_norm_kernel<T, float><<<rows, 256, 0, s>>>(static_cast<T*>(out), out_stride, static_cast<const float*>(x),
+                                                     x_stride, static_cast<const T*>(weight), weight_offset, eps, width);
+    else
+      rms_norm_kernel<T, T><<<rows, 256, 0, s>>>(static_cast<T*>(out), out_stride, static_cast<const T*>(x), x_stride,
+                                                 static_cast<const T*>(weight), weight_offset, eps, width);
+    return check_launch("b200_rms_norm");
+  });
+}
+
+int b200_residual_add2_norm(float* x, const void* a, int64_t a_stride, const void* b, int64_t b_stride, const void* w_next,
+                            float weight_offset, void* out_next, float eps, int rows, int width, int dtype, void* stream) {
+  if (rows < 0 || width <= 0 || width > 40000) return fail(B200_EINVAL, "b200_residual_add2_norm: bad sizes");
+  if (rows == 0) return 0;
+  if (!x || !a || (w_next && !out_next)) return fail(B200_EINVAL, "b200_residual_add2_norm: null pointer");
+  const size_t smem = static_cast<size_t>(width) * sizeof(float);
+  return hybrid_by_dtype(dtype, "b200_residual_add2_norm", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    auto kern = residual_add2_norm_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<rows, 256, smem, static_cast<cudaStream_t>(stream)>>>(x, static_cast<const T*>(a), a_stride,
+                                                                static_cast<const T*>(b), b_stride,
+                                                                static_cast<const T*>(w_next), weight_offset,
+                                                                static_cast<T*>(out_next), eps, width);
+    return check_launch("b200_residual_add2_norm");
+  });
+}
+
+int b200_xielu(void* out, const void* z, int64_t z_stride, const void* pq, int rows, int ff, int dtype, void* stream) {
+  if (rows < 0 || ff <= 0) return fail(B200_EINVAL, "b200_xielu: bad sizes");
+  if (rows == 0) return 0;
+  if (!out || !z || !pq) return fail(B200_EINVAL, "b200_xielu: null pointer");
+  const int64_t total = static_cast<int64_t>(rows) * ff;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  return hybrid_by_dtype(dtype, "b200_xielu", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    xielu_kernel<T><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<T*>(out), static_cast<const T*>(z),
+                                                                         z_stride, static_cast<const T*>(pq), ff, total);
+    return check_launch("b200_xielu");
+  });
+}
+
+int b200_rotary_kv_append(void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
+                          void* k_pool, void* v_pool, const int64_t* slot_mapping, const int32_t* tok_pos, int n_tok, int H,
+                          int G, int dk, int dv, int rot_dims, float rot_base, int rotate_values, int interleaved,
+                          int block_size, int64_t max_blocks, int dtype, void* stream) {
+  if (n_tok < 0 || H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || block_size <= 0 || max_blocks <= 0)
+    return fail(B200_EINVAL, "b200_rotary_kv_append: bad sizes");
+  if (rot_dims < 0 || rot_dims > dk || (rot_dims & 1)) return fail(B200_ESHAPE, "b200_rotary_kv_append: rot_dims %d", rot_dims);
+  if (n_tok == 0) return 0;
+  if (!q || !k || !v || !k_pool || !v_pool || !slot_mapping || !tok_pos) return fail(B200_EINVAL, "b200_rotary_kv_append: null pointer");
+  const size_t smem = sizeof(float) * (static_cast<size_t>(rot_dims) + (rotate_values ? dv : 0) + 4);
+  return hybrid_by_dtype(dtype, "b200_rotary_kv_append", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    rotary_kv_append_kernel<T><<<n_tok, 256, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<T*>(q), q_stride, static_cast<const T*>(k), k_stride, static_cast<const T*>(v), v_stride,
+        static_cast<T*>(k_pool), static_cast<T*>(v_pool), slot_mapping, tok_pos, H, G, dk, dv, rot_dims,
+        static_cast<double>(rot_base), rotate_values, interleaved, block_size);
+    return check_launch("b200_rotary_kv_append");
+  });
+}
+
+int b200_norm_append(const void* x, int64_t x_stride, const void* weight, float weight_offset, float eps, void* pool,
+                     const int64_t* slot_mapping, int n_tok, int width, int dtype, void* stream) {
+  if (n_tok < 0 || width <= 0) return fail(B200_EINVAL, "b200_norm_append: bad sizes");
+  if (n_tok == 0) return 0;
+  if (!x || !weight || !pool || !slot_mapping) return fail(B200_EINVAL, "b200_norm_append: null pointer");
+  return hybrid_by_dtype(dtype, "b200_norm_append", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    norm_append_kernel<T><<<n_tok, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const T*>(x), x_stride, static_cast<const T*>(weight), weight_offset, eps, static_cast<T*>(pool),
+        slot_mapping, width);
+    return check_launch("b200_norm_append");
+  });
+}
+
+int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q, int64_t q_tok_stride,
+                          int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
+                          const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tok_row,
+                          const int32_t* tok_pos, int n_tok, const float* talk, const float* sink, float scale, int window,
+                          int keep_first, int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv,
+                          int block_size, int dtype, void* stream) {
+  if (n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0)
+    return fail(B200_EINVAL, "b200_mixed_paged_attn: bad sizes");
+  if (dv > 512) return fail(B200_ESHAPE, "b200_mixed_paged_attn: value size %d beyond 512", dv);
+  if (n_tok == 0) return 0;
+  if (!out || !q || !k_pool || !v_pool || !block_tables || !tok_row || !tok_pos)
+    return fail(B200_EINVAL, "b200_mixed_paged_attn: null pointer");
+  AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
+             block_tables, table_stride, tok_row, tok_pos, talk, sink, scale, window, keep_first, unrotate, interleaved,
+             static_cast<double>(rot_base), H, G, dk, dv, block_size};
+  const int dvc = dv <= 64 ? 2 : (dv <= 128 ? 4 : (dv <= 256 ? 8 : 16));
+  const int hp = dvc <= 4 ? 8 : (dvc == 8 ? 4 : 2);
+  const int nhs = talk ? H : std::min(hp, H);
+  // the score staging area [warps][nhs][32] is reused for the [hp][dv] results: give it room for both
+  const size_t raw = std::max<size_t>(static_cast<size_t>(kAttnWarpsRow) * nhs * 32, static_cast<size_t>(hp) * dv);
+  const size_t smem = sizeof(float) * (static_cast<size_t>(nhs) * dk + raw + (talk ? static_cast<size_t>(hp) * H : 0) +
+                                       static_cast<size_t>(kAttnWarpsRow) * hp * (dv + 2));
+  if (smem > 200 * 1024) return fail(B200_ESHAPE, "b200_mixed_paged_attn: %zu bytes of shared memory", smem);
+  const dim3 grid(n_tok, (H + hp - 1) / hp);
+  return hybrid_by_dtype(dtype, "b200_mixed_paged_attn", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    auto launch = [&](auto kern) {
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      kern<<<grid, kAttnWarpsRow * 32, smem, static_cast<cudaStream_t>(stream)>>>(A);
+    };
+    if (dvc == 2) launch(mixed_paged_attn_kernel<T, 8, 2>);
+    else if (dvc == 4) launch(mixed_paged_attn_kernel<T, 8, 4>);
+    else if (dvc == 8) launch(mixed_paged_attn_kernel<T, 4, 8>);
+    else launch(mixed_paged_attn_kernel<T, 2, 16>);
+    return check_launch("b200_mixed_paged_attn");
+  });
+}
+
+int b200_causal_conv_silu(void* out, int64_t out_stride, const void* x, int64_t x_stride, const void* w, float* tail,
+                          const int32_t* seqs, int n_seqs, int max_count, int C, int taps, int dtype, void* stream) {
+  if (n_seqs < 0 || C <= 0 || taps < 1 || max_count < 0) return fail(B200_EINVAL, "b200_causal_conv_silu: bad sizes");
+  if (taps > 8) return fail(B200_ESHAPE, "b200_causal_conv_silu: %d taps beyond 8", taps);
+  if (n_seqs == 0 || max_count == 0) return 0;
+  if (!out || !x || !w || !seqs || (taps > 1 && !tail)) return fail(B200_EINVAL, "b200_causal_conv_silu: null pointer");
+  const dim3 grid(n_seqs, (max_count + kConvTokens - 1) / kConvTokens, (C + 127) / 128);
+  return hybrid_by_dtype(dtype, "b200_causal_conv_silu", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    causal_conv_silu_kernel<T><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<T*>(out), out_stride, static_cast<const T*>(x), x_stride, static_cast<const T*>(w), tail,
+        reinterpret_cast<const SeqSpan*>(seqs), C, taps);
+    return check_launch("b200_causal_conv_silu");
+  });
+}
+
+int b200_delta_scan(float* o_raw, const void* q, const void* k, const void* v, int64_t in_stride, const void* beta_logit,
+                    int64_t beta_stride, const void* a_logit, int64_t a_stride, const void* dt_bias, const void* a_log,
+                    float* state, const int32_t* seqs, int n_seqs, int H, int G, int dk, int dv, float unit_eps,
+                    float q_scale, int dtype, void* stream) {
+  if (n_seqs < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_delta_scan: bad sizes");
+  if (dk > 256) return fail(B200_ESHAPE, "b200_delta_scan: key size %d beyond 256", dk);
+  if (n_seqs == 0) return 0;
+  if (!o_raw || !q || !k || !v || !beta_logit || !a_logit || !dt_bias || !a_log || !state || !seqs)
+    return fail(B200_EINVAL, "b200_delta_scan: null pointer");
+  const int dkt = dk <= 32 ? 32 : (dk <= 64 ? 64 : (dk <= 128 ? 128 : 256));
+  const size_t smem = sizeof(float) * kDeltaChunk * (3 * static_cast<size_t>(dkt) + kDeltaCols + 4);
+  const dim3 grid(n_seqs, H, (dv + kDeltaCols - 1) / kDeltaCols);
+  DeltaArgs A{o_raw, q, k, v, in_stride, beta_logit, beta_stride, a_logit, a_stride, dt_bias, a_log, state,
+              reinterpret_cast<const SeqSpan*>(seqs), H, G, dk, dv, unit_eps, q_scale};
+  return hybrid_by_dtype(dtype, "b200_delta_scan", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (dkt == 32) delta_scan_kernel<T, 32><<<grid, kDeltaNT, smem, s>>>(A);
+    else if (dkt == 64) delta_scan_kernel<T, 64><<<grid, kDeltaNT, smem, s>>>(A);
+    else if (dkt == 128) delta_scan_kernel<T, 128><<<grid, kDeltaNT, smem, s>>>(A);
+    else delta_scan_kernel<T, 256><<<grid, kDeltaNT, smem, s>>>(A);
+    return check_launch("b200_delta_scan");
+  });
+}
+
+int b200_head_rmsnorm_gated(void* out, const float* x, const void* weight, const void* gate, int64_t gate_stride, float eps,
+                            int64_t n_tok, int H, int dv, int dtype, void* stream) {
+  if (n_tok < 0 || H <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_head_rmsnorm_gated: bad sizes");
+  if (n_tok == 0) return 0;
+  if (!out || !x || !weight) return fail(B200_EINVAL, "b200_head_rmsnorm_gated: null pointer");
+  const int64_t rows = n_tok * H;
+  return hybrid_by_dtype(dtype, "b200_head_rmsnorm_gated", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    head_rmsnorm_gated_kernel<T><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<T*>(out), x, static_cast<const T*>(weight), static_cast<const T*>(gate), gate_stride, eps, rows, H, dv);
+    return check_launch("b200_head_rmsnorm_gated");
+  });
+}
+
+}  // extern "C"

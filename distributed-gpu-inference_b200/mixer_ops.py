@@ -299,3 +299,186 @@ def expert_combine(ys: torch.Tensor, where: torch.Tensor, n_tok: int, top: int) 
                                      DTYPE_ID[ys.dtype], _stream())
     _lib.check_mixers(rc, "b200_expert_combine")
     return out
+
+
+# ---- pieces for hybrid designs (csrc/b200_hybrid_ops.cu) ---------------------------------------------------------------
+@_timed
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, weight_offset: float = 0.0) -> torch.Tensor:
+    """``x * rsqrt(mean(x^2) + eps) * (weight_offset + weight)`` over the last dimension of 2-D rows (fp32 or the
+    weight's dtype, column slices are fine); the weight's dtype out."""
+    _need_cuda(x, weight)
+    if x.dtype not in (torch.float32, weight.dtype) or weight.numel() != x.shape[1]:
+        raise ValueError("x must be fp32 or of the weight's dtype, [rows, width] with width = weight.numel()")
+    out = torch.empty(x.shape, dtype=weight.dtype, device=x.device)
+    rc = _lib_().b200_rms_norm(out.data_ptr(), out.shape[1], x.data_ptr(), _rows2(x),
+                               int(x.dtype == torch.float32 and weight.dtype != torch.float32), weight.data_ptr(),
+                               float(weight_offset), float(eps), x.shape[0], x.shape[1], DTYPE_ID[weight.dtype], _stream())
+    _lib.check_mixers(rc, "b200_rms_norm")
+    return out
+
+
+@_timed
+def residual_add2_norm(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor], w_next: Optional[torch.Tensor],
+                       eps: float, weight_offset: float = 0.0) -> Optional[torch.Tensor]:
+    """In place ``x += (a + b)`` on the fp32 residual (``b`` may be None); returns ``rms_norm(x; w_next)`` in the
+    branches' dtype when ``w_next`` is given."""
+    _need_cuda(x, a)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2 or a.shape != x.shape:
+        raise ValueError("x must be contiguous fp32 [rows, width] and the branches of the same shape")
+    if b is not None and (b.shape != x.shape or b.dtype != a.dtype):
+        raise ValueError("both branches must have one shape and dtype")
+    out = torch.empty(x.shape, dtype=a.dtype, device=x.device) if w_next is not None else None
+    rc = _lib_().b200_residual_add2_norm(x.data_ptr(), a.data_ptr(), _rows2(a), _ptr(b), _rows2(b) if b is not None else 0,
+                                         _ptr(w_next), float(weight_offset), _ptr(out), float(eps), x.shape[0], x.shape[1],
+                                         DTYPE_ID[a.dtype], _stream())
+    _lib.check_mixers(rc, "b200_residual_add2_norm")
+    return out
+
+
+@_timed
+def xielu(z: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
+    """``z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` with ``pq = (p, q)``."""
+    _need_cuda(z, pq)
+    if pq.numel() != 2 or pq.dtype != z.dtype:
+        raise ValueError("pq holds the two numbers (p, q) in the activations' dtype")
+    out = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+    rc = _lib_().b200_xielu(out.data_ptr(), z.data_ptr(), _rows2(z), pq.data_ptr(), z.shape[0], z.shape[1],
+                            DTYPE_ID[z.dtype], _stream())
+    _lib.check_mixers(rc, "b200_xielu")
+    return out
+
+
+@_timed
+def rotary_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                     slot_mapping: torch.Tensor, tok_pos: torch.Tensor, H: int, rot_dims: int, rot_base: float,
+                     rotate_values: bool, interleaved: bool = False) -> None:
+    """Rotary positions on q (in place) and k over their first ``rot_dims`` dimensions, optionally the values turned
+    over their whole width; k and v are stored in the pools at ``slot_mapping``."""
+    _need_cuda(q, k, v, k_pool, v_pool, slot_mapping, tok_pos)
+    nb, G, bs, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    n = q.shape[0]
+    if q.shape[1] != H * dk or k.shape != (n, G * dk) or v.shape != (n, G * dv):
+        raise ValueError("q / k / v do not match the pools")
+    if slot_mapping.dtype != torch.int64 or tok_pos.dtype != torch.int32:
+        raise TypeError("slot_mapping is int64, tok_pos int32")
+    rc = _lib_().b200_rotary_kv_append(q.data_ptr(), _rows2(q), k.data_ptr(), _rows2(k), v.data_ptr(), _rows2(v),
+                                       k_pool.data_ptr(), v_pool.data_ptr(), slot_mapping.data_ptr(), tok_pos.data_ptr(),
+                                       n, H, G, dk, dv, int(rot_dims), float(rot_base), int(rotate_values),
+                                       int(interleaved), bs, nb, DTYPE_ID[k_pool.dtype], _stream())
+    _lib.check_mixers(rc, "b200_rotary_kv_append")
+
+
+@_timed
+def norm_append(x: torch.Tensor, weight: torch.Tensor, eps: float, pool: torch.Tensor, slot_mapping: torch.Tensor,
+                weight_offset: float = 0.0) -> None:
+    """``pool[slot] = rms_norm(x[n]; weight)``: latent rows into a one-head pool ``[blocks, 1, bs, width]``."""
+    _need_cuda(x, weight, pool, slot_mapping)
+    if pool.shape[1] != 1 or pool.shape[3] != x.shape[1] or x.dtype != pool.dtype or slot_mapping.dtype != torch.int64:
+        raise ValueError("the pool must be [blocks, 1, block size, width] in the rows' dtype; slots int64")
+    rc = _lib_().b200_norm_append(x.data_ptr(), _rows2(x), weight.data_ptr(), float(weight_offset), float(eps),
+                                  pool.data_ptr(), slot_mapping.data_ptr(), x.shape[0], x.shape[1], DTYPE_ID[x.dtype],
+                                  _stream())
+    _lib.check_mixers(rc, "b200_norm_append")
+
+
+@_timed
+def mixed_paged_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                          block_tables: torch.Tensor, tok_row: torch.Tensor, tok_pos: torch.Tensor, scale: float,
+                          talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
+                          keep_first: int = 0, unrotate_base: Optional[float] = None, interleaved: bool = False,
+                          gate: Optional[torch.Tensor] = None) -> None:
+    """Softmax attention of packed query rows over the paged cache.  ``q`` and ``out`` are 3-D ``[n, H, dk | dv]``
+    VIEWS with a contiguous last dimension (any token / head strides); ``talk`` fp32 ``[H, H]`` mixes the heads'
+    scores before the softmax, ``sink`` fp32 ``[H]`` adds exp(sink) to the denominator, ``window`` > 0 limits a
+    position to its last ``window`` tokens plus the sequence's first ``keep_first``, ``unrotate_base`` turns the
+    output back by the position over the value width, ``gate`` ``[n, H]`` is a sigmoid gate per head."""
+    _need_cuda(out, q, k_pool, v_pool, block_tables, tok_row, tok_pos)
+    nb, G, bs, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    n, H = q.shape[0], q.shape[1]
+    if q.dim() != 3 or q.shape[2] != dk or tuple(out.shape) != (n, H, dv) or q.stride(2) != 1 or out.stride(2) != 1:
+        raise ValueError("q must be [n, H, dk] and out [n, H, dv] with contiguous last dimensions")
+    if out.dtype != q.dtype or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+        raise TypeError("q, out and the pools share one dtype")
+    for t in (block_tables, tok_row, tok_pos):
+        if t.dtype != torch.int32:
+            raise TypeError("block tables, token rows and positions are int32")
+    for t, shape in ((talk, (H, H)), (sink, (H,))):
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous()):
+            raise ValueError("talk is contiguous fp32 [H, H], sink fp32 [H]")
+    if gate is not None and (tuple(gate.shape) != (n, H) or gate.dtype != q.dtype):
+        raise ValueError("gate must be [n, H] in the activations' dtype")
+    rc = _lib_().b200_mixed_paged_attn(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
+                                       _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
+                                       v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), tok_row.data_ptr(),
+                                       tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink), float(scale), int(window),
+                                       int(keep_first), int(unrotate_base is not None), int(interleaved),
+                                       float(unrotate_base or 0.0), H, G, dk, dv, bs, DTYPE_ID[q.dtype], _stream())
+    _lib.check_mixers(rc, "b200_mixed_paged_attn")
+
+
+@_timed
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, tail: torch.Tensor, seqs: torch.Tensor,
+                     max_count: int) -> torch.Tensor:
+    """Short causal convolution per channel over each sequence's tokens, then SiLU.  ``x [n, C]`` (a column slice is
+    fine), ``weight [C, taps]`` (last column = the current token), ``tail`` fp32 ``[slots, taps - 1, C]`` carries each
+    live sequence's last inputs between steps and is updated."""
+    _need_cuda(x, weight, tail, seqs)
+    C, taps = weight.shape
+    if x.shape[1] != C or tail.dtype != torch.float32 or tuple(tail.shape[1:]) != (taps - 1, C) or not tail.is_contiguous():
+        raise ValueError("x [n, C], weight [C, taps], tail fp32 [slots, taps - 1, C]")
+    if seqs.dtype != torch.int32 or seqs.dim() != 2 or seqs.shape[1] != 4 or not seqs.is_contiguous():
+        raise ValueError("seqs must be contiguous int32 [n_seqs, 4]")
+    out = torch.empty((x.shape[0], C), dtype=x.dtype, device=x.device)
+    rc = _lib_().b200_causal_conv_silu(out.data_ptr(), C, x.data_ptr(), _rows2(x), weight.data_ptr(), tail.data_ptr(),
+                                       seqs.data_ptr(), seqs.shape[0], int(max_count), C, taps, DTYPE_ID[x.dtype], _stream())
+    _lib.check_mixers(rc, "b200_causal_conv_silu")
+    return out
+
+
+@_timed
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta_logit: torch.Tensor, a_logit: torch.Tensor,
+               dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, seqs: torch.Tensor, G: int,
+               unit_eps: float, q_scale: float) -> torch.Tensor:
+    """Gated delta rule with a decay per key channel over each sequence's tokens; ``state`` fp32 ``[slots, H, dk, dv]``
+    is read (unless the sequence is fresh) and written back.  ``q / k [n, G*dk]`` and ``v [n, H*dv]`` are column
+    slices of ONE tensor (same row stride), ``beta_logit [n, H]``, ``a_logit [n, H*dk]``.  Returns fp32 ``[n, H, dv]``."""
+    _need_cuda(q, k, v, beta_logit, a_logit, dt_bias, a_log, state, seqs)
+    n = q.shape[0]
+    _, H, dk, dv = state.shape
+    if q.shape[1] != G * dk or k.shape != q.shape or v.shape != (n, H * dv) or beta_logit.shape != (n, H) \
+            or a_logit.shape != (n, H * dk) or dt_bias.numel() != H * dk or a_log.numel() != H:
+        raise ValueError("inputs do not match the state's shape")
+    stride = _rows2(q)
+    if n > 1 and (k.stride(0) != stride or v.stride(0) != stride):
+        raise ValueError("q, k and v must share a row stride")
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise TypeError("the recurrent state is contiguous fp32")
+    if seqs.dtype != torch.int32 or seqs.dim() != 2 or seqs.shape[1] != 4 or not seqs.is_contiguous():
+        raise ValueError("seqs must be contiguous int32 [n_seqs, 4]")
+    o = torch.empty((n, H, dv), dtype=torch.float32, device=q.device)
+    rc = _lib_().b200_delta_scan(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), stride, beta_logit.data_ptr(),
+                                 _rows2(beta_logit), a_logit.data_ptr(), _rows2(a_logit), dt_bias.data_ptr(),
+                                 a_log.data_ptr(), state.data_ptr(), seqs.data_ptr(), seqs.shape[0], H, G, dk, dv,
+                                 float(unit_eps), float(q_scale), DTYPE_ID[q.dtype], _stream())
+    _lib.check_mixers(rc, "b200_delta_scan")
+    return o
+
+
+@_timed
+def head_rmsnorm_gated(x: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    """fp32 ``[n, H, dv]`` -> ``x * rsqrt(mean(x^2) + eps) * weight * sigmoid(gate)`` as ``[n, H*dv]`` in the weight's
+    dtype; ``gate [n, H*dv]`` holds logits."""
+    _need_cuda(x, weight)
+    n, H, dv = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or weight.numel() != dv:
+        raise ValueError("x must be contiguous fp32 [n, H, dv] and weight [dv]")
+    if gate is not None and (tuple(gate.shape) != (n, H * dv) or gate.dtype != weight.dtype):
+        raise ValueError("gate must be [n, H*dv] in the weight's dtype")
+    out = torch.empty((n, H * dv), dtype=weight.dtype, device=x.device)
+    rc = _lib_().b200_head_rmsnorm_gated(out.data_ptr(), x.data_ptr(), weight.data_ptr(), _ptr(gate),
+                                         _rows2(gate) if gate is not None else 0, float(eps), n, H, dv,
+                                         DTYPE_ID[weight.dtype], _stream())
+    _lib.check_mixers(rc, "b200_head_rmsnorm_gated")
+    return out

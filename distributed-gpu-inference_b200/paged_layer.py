@@ -177,6 +177,7 @@ class RaggedBatchState:
     slot_mapping   int64 [N]              pool slot of each token (block * block_size + offset)
     block_tables   int32 [B, max_blocks]  pool blocks per live sequence of the step
     scan_seqs      int32 [B, 4]           (first row, token count, recurrent-state slot, 1 if the sequence starts here)
+    tok_row        int32 [N]              row of ``block_tables`` each token belongs to
     spans          host list of (first row, token count, block-table row, tokens of the sequence before this step)
     v_first        values the first value-mixing attention layer stored for this step's tokens (set by that layer)
     pending_norm   the next sublayer's normed input when the previous layer already computed it in its epilogue
@@ -187,6 +188,7 @@ class RaggedBatchState:
     block_tables: torch.Tensor
     scan_seqs: torch.Tensor
     spans: list
+    tok_row: Optional[torch.Tensor] = None
     v_first: Optional[torch.Tensor] = None
     pending_norm: Optional[torch.Tensor] = None
     _tiles: Optional[dict] = None

@@ -204,6 +204,7 @@ class RaggedStepEngine:
             block_tables=up(tables),
             scan_seqs=up(np.asarray(scans, dtype=np.int32)),
             spans=spans,
+            tok_row=up(np.repeat(np.arange(len(spans), dtype=np.int32), [sp[1] for sp in spans])),
         )
         h = up(np.asarray(ids, dtype=np.int64))
         for si, shard in enumerate(self.shards):

@@ -486,7 +486,9 @@ class RecurrentStatePool:
     """Fixed-size fp32 state per live sequence for layers that carry a recurrence instead of keys and values.
 
     ``shapes[i]`` is the state shape of recurrent layer ``i`` (for a gated linear recurrence: ``(heads, key size,
-    value size)``); layer ``i`` owns one tensor ``[slots, *shapes[i]]``.  A sequence takes ONE slot number, valid in
+    value size)``); layer ``i`` owns one tensor ``[slots, *shapes[i]]``.  A layer that carries several things (a
+    recurrence's state and a short convolution's last inputs, say) gives a LIST of shapes and owns a tuple of
+    tensors, all indexed by the same slot.  A sequence takes ONE slot number, valid in
     every layer, at admission and gives it back at its end.  Slots are reused last-freed-first; a slot's content is
     whatever its last owner left, so the first step of a sequence must start from zero (the scan kernels take a
     ``fresh`` flag per sequence; ``reset`` zeroes a slot explicitly).  There is no reference counterpart: the
@@ -495,10 +497,16 @@ class RecurrentStatePool:
 
     def __init__(self, shapes: Sequence[Sequence[int]], slots: int, device: str = "cuda"):
         self.slots = slots
-        self.shapes = [tuple(int(d) for d in s) for s in shapes]
         self.device = device
-        self.states: List[torch.Tensor] = [torch.zeros((slots,) + s, dtype=torch.float32, device=device)
-                                           for s in self.shapes]
+
+        def make(shape):
+            return torch.zeros((slots,) + tuple(int(d) for d in shape), dtype=torch.float32, device=device)
+
+        # an entry whose first element is itself a shape is a group of tensors for one layer
+        self.shapes = [tuple(tuple(int(d) for d in part) for part in s) if s and not isinstance(s[0], int)
+                       else tuple(int(d) for d in s) for s in shapes]
+        self.states: List[Any] = [tuple(make(part) for part in s) if s and not isinstance(s[0], int) else make(s)
+                                  for s in self.shapes]
         self._free: List[int] = list(range(slots - 1, -1, -1))
         self._live: Dict[int, bool] = {}
 
@@ -514,11 +522,16 @@ class RecurrentStatePool:
             raise ValueError(f"state slot {slot} is not live")
         self._free.append(slot)
 
-    def reset(self, slot: int) -> None:
+    def _tensors(self):
         for t in self.states:
+            yield from (t if isinstance(t, tuple) else (t,))
+
+    def reset(self, slot: int) -> None:
+        for t in self._tensors():
             t[slot].zero_()
 
-    def layer(self, idx: int) -> torch.Tensor:
+    def layer(self, idx: int):
+        """The layer's state tensor, or its tuple of tensors when it was declared with a list of shapes."""
         return self.states[idx]
 
     @property
@@ -526,7 +539,7 @@ class RecurrentStatePool:
         return len(self._free)
 
     def get_total_memory_gb(self) -> float:
-        return sum(t.numel() * 4 for t in self.states) / (1024 ** 3)
+        return sum(t.numel() * 4 for t in self._tensors()) / (1024 ** 3)
 
 
 class DistributedKVCacheManager:

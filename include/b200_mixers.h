@@ -111,6 +111,72 @@ int b200_clamped_glu(void* y, const void* gu, int64_t rows, int ff, float limit,
 int b200_expert_combine(float* out, const void* ys, const int64_t* where, int64_t n_tok, int top, int width, int dtype,
                         void* stream);
 
+/* ---- pieces for hybrid designs: one norm per layer, mixer and feed-forward added to the residual together ---------- */
+
+/* SeqSpan rows used below: int32 [n_seqs, 4] = (first packed row, token count, state slot, fresh); fresh != 0: the
+ * sequence starts in this step and its carried state counts as zero. */
+
+/* out[r] = x[r] * rsqrt(mean(x[r]^2) + eps) * (weight_offset + weight); x rows are fp32 (x_is_f32) or T, with row
+ * strides in elements; out T. */
+int b200_rms_norm(void* out, int64_t out_stride, const void* x, int64_t x_stride, int x_is_f32, const void* weight,
+                  float weight_offset, float eps, int rows, int width, int dtype, void* stream);
+
+/* x[r] += (a[r] + b[r]) in fp32, in place (b may be NULL); with w_next, out_next[r] = rms_norm(x[r]; w_next) in T. */
+int b200_residual_add2_norm(float* x, const void* a, int64_t a_stride, const void* b, int64_t b_stride, const void* w_next,
+                            float weight_offset, void* out_next, float eps, int rows, int width, int dtype, void* stream);
+
+/* xIELU: z > 0: softplus(p) z^2 + z/2;  z <= 0: (1/2 + softplus(q)) (exp(z) - 1 - z) + z/2;  pq = (p, q) in T. */
+int b200_xielu(void* out, const void* z, int64_t z_stride, const void* pq, int rows, int ff, int dtype, void* stream);
+
+/* Rotary positions on the first rot_dims dimensions of every q head (in place) and k head, pair (i, i + rot_dims/2)
+ * (interleaved: (2i, 2i + 1)) turned by pos * rot_base^(-2i / rot_dims); with rotate_values, the values are turned the
+ * same way over their whole width dv by pos * rot_base^(-2m / dv).  k and v go to the pools ([max_blocks, G, block_size,
+ * dk | dv]) at slot_mapping (negative = skip).  Angles are formed in double precision. */
+int b200_rotary_kv_append(void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
+                          void* k_pool, void* v_pool, const int64_t* slot_mapping, const int32_t* tok_pos, int n_tok, int H,
+                          int G, int dk, int dv, int rot_dims, float rot_base, int rotate_values, int interleaved,
+                          int block_size, int64_t max_blocks, int dtype, void* stream);
+
+/* pool[slot] = rms_norm(x[n]; weight): latent rows of `width` into a one-head pool [max_blocks, 1, block_size, width]. */
+int b200_norm_append(const void* x, int64_t x_stride, const void* weight, float weight_offset, float eps, void* pool,
+                     const int64_t* slot_mapping, int n_tok, int width, int dtype, void* stream);
+
+/* Softmax attention of packed query rows over the paged cache (which already holds this step's keys and values).
+ *   raw(h, i, j)   = (q_ih . k_j) * scale                      k of kv head h / (H / G)
+ *   score(h, i, j) = sum_g talk[h][g] raw(g, i, j)              (talk NULL: score = raw)
+ *   visible        : j <= i and (window <= 0 or i - j < window or j < keep_first)
+ *   out(i, h)      = sum_j exp(score) v_j / (sum_j exp(score) + exp(sink[h]))     (sink NULL: no extra term)
+ * With unrotate, pair m of out(i, h) is turned by -pos_i * rot_base^(-2m / dv) (the inverse of the rotation the
+ * values were stored with); with gate, out(i, h) *= sigmoid(gate[i][h]).  q element (n, h, d) is at
+ * n * q_tok_stride + h * q_head_stride + d, the output likewise; tok_row[n] is the token's row of block_tables. */
+int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q, int64_t q_tok_stride,
+                          int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
+                          const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tok_row,
+                          const int32_t* tok_pos, int n_tok, const float* talk, const float* sink, float scale, int window,
+                          int keep_first, int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv,
+                          int block_size, int dtype, void* stream);
+
+/* out[t, c] = silu(sum_i w[c][i] * x[t - (taps - 1 - i), c]) per sequence (SeqSpan rows); inputs before the portion
+ * come from tail [slots, taps - 1, C] (fp32, oldest first), which then receives the portion's last taps - 1 inputs. */
+int b200_causal_conv_silu(void* out, int64_t out_stride, const void* x, int64_t x_stride, const void* w, float* tail,
+                          const int32_t* seqs, int n_seqs, int max_count, int C, int taps, int dtype, void* stream);
+
+/* Gated delta rule per (sequence, head) over the sequence's tokens of this step, in order:
+ *   q <- q / sqrt(sum q^2 + unit_eps) * q_scale, k <- k / sqrt(sum k^2 + unit_eps)          (per head)
+ *   g = exp(-exp(a_log[h]) * softplus(a_logit + dt_bias)) [dk], beta = sigmoid(beta_logit)
+ *   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+ * q, k: T rows of G*dk (value head h reads head h / (H / G)), v: T rows of H*dv, all with row stride in_stride;
+ * a_logit: T [n, H*dk]; state fp32 [slots, H, dk, dv]; o_raw fp32 [n_tok, H, dv]. */
+int b200_delta_scan(float* o_raw, const void* q, const void* k, const void* v, int64_t in_stride, const void* beta_logit,
+                    int64_t beta_stride, const void* a_logit, int64_t a_stride, const void* dt_bias, const void* a_log,
+                    float* state, const int32_t* seqs, int n_seqs, int H, int G, int dk, int dv, float unit_eps,
+                    float q_scale, int dtype, void* stream);
+
+/* out[n, h, :] = x[n, h, :] * rsqrt(mean(x^2) + eps) * weight * sigmoid(gate[n, h, :]); x fp32 [n_tok, H, dv],
+ * gate T rows of H*dv (NULL: no gate), out T [n_tok, H*dv]. */
+int b200_head_rmsnorm_gated(void* out, const float* x, const void* weight, const void* gate, int64_t gate_stride, float eps,
+                            int64_t n_tok, int H, int dv, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
