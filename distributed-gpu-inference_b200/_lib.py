@@ -137,13 +137,18 @@ MIXER_SIGNATURES = {
     "b200_xielu": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200_rotary_kv_append": (
         c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int64, c_int, c_void_p]),
+                c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_int64, c_void_p, c_int, c_void_p]),
     "b200_norm_append": (
         c_int, [c_void_p, c_int64, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200_mixed_paged_attn": (
         c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_float, c_int,
                 c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_mixed_prompt_attn_supported": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "b200_mixed_prompt_attn": (
+        c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                c_int, c_int, c_int, c_int, c_void_p]),
     "b200_causal_conv_silu": (
         c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                 c_void_p]),

@@ -5,6 +5,10 @@ of every mixer kernel of one prompt step and one decode step against its memory 
 Random weights, synthetic token ids; bf16.  Timed with CUDA events on the launching stream after warm-up; the
 inputs of a step (activations, weights, KV of all sequences) exceed L2 at the two larger sizes and the report says
 so per size.  One JSON line on stdout; the default workload and output line of bench.py are untouched.
+
+``bench.py --compare sanesun``: the same two steps for the Sanesun model class beside a Petipel model of equal width,
+depth, head layout and feed-forward size (its closest relative here: attention layers alternating with a recurrence
+on the same engine), with every kernel of both against its floor so that like kernels can be read side by side.
 """
 from __future__ import annotations
 
@@ -186,6 +190,142 @@ def _kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> Dict[str,
             "clamped_glu": (n_tok * s["top"] * s["eff"] * 6, 0),
             "scaled_gather": (n_tok * s["top"] * W * 4, 0),
             "expert_combine": (n_tok * s["top"] * W * 2 + n_tok * W * 4, 0),
+        }
+        for name, ts in by.items():
+            t = statistics.mean(ts)
+            entry = {"us": round(t * 1e6, 1), "calls": len(ts)}
+            if name in floors:
+                nbytes, flops = floors[name]
+                floor = max(nbytes / hbm, flops / tf)
+                entry["of_floor"] = round(floor / t, 3)
+                entry["bound"] = "math" if flops / tf > nbytes / hbm else "memory"
+            out.setdefault(phase, {})[name] = entry
+    return out
+
+
+# ---- Sanesun beside Petipel ------------------------------------------------------------------------------------------
+SANESUN_WINDOW, SANESUN_KEEP, LATENT_RANK = 512, 4, 256
+
+
+def sanesun_config(s: Dict[str, int]) -> Dict[str, Any]:
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv"], "dim": s["dk"], "vdim": s["dv"],
+                                          "scale": 1.0 / math.sqrt(s["dk"]),
+                                          "mask": {"size": SANESUN_WINDOW, "keep_first": SANESUN_KEEP},
+                                          "rot": {"base": 10000.0, "dims": s["dk"] // 2}}}
+    lat = {"type": "latent_attention", "mixer": {"heads": s["heads"], "dim": s["dk"], "vdim": s["dv"],
+                                                 "kv_rank": LATENT_RANK, "q_rank": s["width"] // 2,
+                                                 "scale": 1.0 / math.sqrt(s["dk"])}}
+    rec = {"type": "channel_delta", "mixer": {"heads": s["rheads"], "kv_heads": s["rheads"], "dim": s["rdk"],
+                                              "vdim": s["rdv"], "conv": 4}}
+    layers = [dict(m, mlp={"kind": "dense", "ff": s["ff"]}) for m in (rec, att, rec, lat)]
+    return {"architecture": "Sanesun", "width": s["width"], "vocab": VOCAB, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def petipel_dense_config(s: Dict[str, int]) -> Dict[str, Any]:
+    raw = petipel_config(s)
+    for layer in raw["layers"]:
+        layer["mlp"] = {"kind": "dense", "ff": s["ff"]}
+    return raw
+
+
+def run_sanesun(args, measured_peaks, ClockSampler) -> None:
+    from . import mixer_ops
+    from . import petipel_layer as P
+    from . import sanesun_layer as S
+    from .ragged_engine import RaggedStepEngine
+
+    dev = "cuda:0"
+    peaks, how = measured_peaks()
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    steps, warmup = max(3, args.steps), max(3, args.warmup)
+    B, Pn, ctx, Bd = 8, 2048, 2048, 64
+    g = torch.Generator().manual_seed(0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    report: Dict[str, Any] = {}
+    for name, s in SIZES.items():
+        if args.compare_sizes and name not in args.compare_sizes.split(","):
+            continue
+        row: Dict[str, Any] = {}
+        prompts = torch.randint(0, VOCAB, (Bd, ctx), generator=g).tolist()
+        for label, mod, raw in (("sanesun", S, sanesun_config(s)), ("petipel", P, petipel_dense_config(s))):
+            cfg = (S.SanesunConfig if mod is S else P.PetipelConfig).from_dict(raw)
+            shards = mod.build_shards(cfg, mod.random_checkpoint(cfg, seed=0), [(0, LAYERS)], dev, torch.bfloat16)
+            eng = RaggedStepEngine(shards, max_tokens=Bd * (ctx + 64), max_seqs=Bd, fp32_logits=False)
+
+            def prompt_step():
+                eng.step([(i, prompts[i][:Pn], [Pn - 1]) for i in range(B)])
+                for i in range(B):
+                    eng.finish(i)
+
+            ms = _time_steps(prompt_step, steps, warmup)
+            row[label + "_prefill_tok_s"] = round(B * Pn / ms * 1e3)
+            mixer_ops.EVENTS = []
+            prompt_step()
+            torch.cuda.synchronize()
+            ev_prompt, mixer_ops.EVENTS = mixer_ops.EVENTS, None
+            for i in range(0, Bd, B):
+                eng.step([(j, prompts[j], []) for j in range(i, i + B)])
+            nxt = [[1] for _ in range(Bd)]
+
+            def decode_step():
+                eng.step([(j, nxt[j], [0]) for j in range(Bd)])
+
+            n_dec = min(steps, 32)
+            ms = _time_steps(decode_step, n_dec, warmup)
+            row[label + "_decode_tok_s"] = round(Bd / ms * 1e3)
+            mixer_ops.EVENTS = []
+            decode_step()
+            torch.cuda.synchronize()
+            ev_decode, mixer_ops.EVENTS = mixer_ops.EVENTS, None
+            eng.release()
+            table = _kernel_table if mod is P else _sanesun_kernel_table
+            row[label + "_kernels"] = table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx + warmup + n_dec, hbm, tf)
+            del eng, shards
+            torch.cuda.empty_cache()
+        row["inputs_exceed_l2"] = bool(Bd * ctx * s["kv"] * (s["dk"] + s["dv"]) * 2 > 126e6)
+        report[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"bench": "sanesun_vs_petipel", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                      "layers": LAYERS, "prompt_step": f"{B} x {Pn} tokens", "decode_step": f"{Bd} sequences at {ctx}",
+                      "peaks": how, "sizes": report, "clocks": clocks}), flush=True)
+
+
+def _sanesun_kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> Dict[str, Any]:
+    """Like ``_kernel_table`` for the Sanesun kernels.  The two attention layers share one kernel; their calls are
+    told apart by their order in a step (layer 1: windowed, layer 3: latent) and reported under two names."""
+    out: Dict[str, Any] = {}
+    W, H, G, dk, dv = s["width"], s["heads"], s["kv"], s["dk"], s["dv"]
+    RH, rdk, rdv, r = s["rheads"], s["rdk"], s["rdv"], LATENT_RANK
+    C = 2 * RH * rdk + RH * rdv
+    for phase, events, n_tok, past in (("prompt", ev_prompt, B * Pn, 0), ("decode", ev_decode, Bd, ctx)):
+        by: Dict[str, List[float]] = {}
+        seen_attn = 0
+        for name, a, b in events:
+            if name == "mixed_paged_attention":
+                name = ("windowed_attention", "latent_attention")[seen_attn % 2]
+                seen_attn += 1
+            by.setdefault(name, []).append(a.elapsed_time(b) * 1e-3)
+        per_seq = n_tok // (B if phase == "prompt" else Bd)
+        n_seq = n_tok // per_seq
+        # keys a query sees: all earlier ones (latent), or the window and the kept prefix (windowed)
+        pairs_full = per_seq * past + per_seq * (per_seq + 1) // 2
+        seen_w = [min(past + t + 1, SANESUN_WINDOW + SANESUN_KEEP) for t in range(per_seq)]
+        pairs_win = sum(seen_w)
+        keys_win = min(past + per_seq, (SANESUN_WINDOW + SANESUN_KEEP + per_seq))
+        floors = {
+            "rms_norm": (n_tok * W * 6, 0),
+            "residual_add2_norm": (n_tok * W * (4 + 4 + 2 + 2 + 2), 0),
+            "xielu": (n_tok * s["ff"] * 4, 0),
+            "rotary_kv_append": (n_tok * (H * dk * 2 + G * (dk + dv) * 2) * 2, 0),
+            "norm_append": (n_tok * r * 4, 0),
+            "windowed_attention": (n_seq * keys_win * G * (dk + dv) * 2 + n_tok * H * (dk + dv) * 2,
+                                   n_seq * H * 2 * (dk + dv) * pairs_win),
+            "latent_attention": (n_seq * (past + per_seq) * r * 2 + n_tok * H * 2 * r * 2, n_seq * H * 2 * 2 * r * pairs_full),
+            "causal_conv_silu": (n_tok * C * 4, 0),
+            "delta_scan": (n_tok * RH * (3 * rdk + rdv) * 2 + n_tok * RH * rdv * 4 + 2 * n_seq * RH * rdk * rdv * 4, 0),
+            "head_rmsnorm_gated": (n_tok * RH * rdv * 8, 0),
         }
         for name, ts in by.items():
             t = statistics.mean(ts)

@@ -128,7 +128,8 @@ __global__ void __launch_bounds__(256)
 rotary_kv_append_kernel(T* __restrict__ q, int64_t q_stride, const T* __restrict__ k, int64_t k_stride,
                         const T* __restrict__ v, int64_t v_stride, T* __restrict__ k_pool, T* __restrict__ v_pool,
                         const int64_t* __restrict__ slot_mapping, const int32_t* __restrict__ tok_pos, int H, int G, int dk,
-                        int dv, int rot_dims, double rot_base, int rotate_values, int interleaved, int block_size) {
+                        int dv, int rot_dims, double rot_base, int rotate_values, int interleaved, int block_size,
+                        float* __restrict__ value_rot) {
   extern __shared__ float tab[];   // cos_qk[rh] sin_qk[rh] cos_v[vh] sin_v[vh]
   const int n = blockIdx.x;
   const int rh = rot_dims / 2, vh = rotate_values ? dv / 2 : 0;
@@ -143,8 +144,17 @@ rotary_kv_append_kernel(T* __restrict__ q, int64_t q_stride, const T* __restrict
     const double a = p * pow(rot_base, -2.0 * m / static_cast<double>(is_v ? dv : rot_dims));
     double s, c;
     sincos(a, &s, &c);
-    if (is_v) { cv[m] = static_cast<float>(c); sv[m] = static_cast<float>(s); }
-    else { cq[m] = static_cast<float>(c); sq[m] = static_cast<float>(s); }
+    if (is_v) {
+      cv[m] = static_cast<float>(c);
+      sv[m] = static_cast<float>(s);
+      if (value_rot) {   // the attention kernel turns its outputs back with the same numbers
+        value_rot[(static_cast<int64_t>(n) * vh + m) * 2] = cv[m];
+        value_rot[(static_cast<int64_t>(n) * vh + m) * 2 + 1] = sv[m];
+      }
+    } else {
+      cq[m] = static_cast<float>(c);
+      sq[m] = static_cast<float>(s);
+    }
   }
   __syncthreads();
   const int64_t slot = slot_mapping[n];
@@ -429,6 +439,344 @@ mixed_paged_attn_kernel(const AttnArgs A) {
   }
 }
 
+// ---- mixed-head paged attention on the tensor cores (16-bit storage types) -----------------------------------------
+// A CTA serves up to 16 consecutive tokens of one sequence (one m16 row block) and up to 8 * HW query heads: warp w
+// owns heads w * HW .. w * HW + HW - 1 of the CTA's range.  Keys are walked in tiles of 32 at absolute multiples of 32,
+// skipping the tiles a window hides; the K and V rows of a tile (every kv head the CTA needs) arrive in shared memory
+// by cp.async with zero fill past the sequence's end.  S = Q K^T and O += P V are mma.sync m16n8k16 with fp32
+// accumulators; the softmax runs in fp32 on the S fragments and only the weights P are rounded to the storage type as
+// the left operand of P V.  With a head-mixing matrix the CTA's warps first form the raw scores of ALL heads into
+// shared memory and every warp then mixes the rows of its own heads from there.  When keys and values are the same
+// pool (a latent attention) and equally wide, one staged tile serves both products.  Outputs that have to be turned
+// back pass a per-warp fp32 slab in shared memory, where a pair's two halves meet.
+template <typename T>
+struct Mma16x8;
+template <>
+struct Mma16x8<__nv_bfloat16> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+};
+template <>
+struct Mma16x8<__half> {
+  static __device__ __forceinline__ void mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    const __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+};
+
+__device__ __forceinline__ void stage16(void* smem_dst, const void* gmem_src, bool valid) {
+  const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  const int bytes = valid ? 16 : 0;   // no source bytes: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
+}
+
+constexpr int kTcWarps = 8;
+constexpr int kTcKeys = 32;
+constexpr int kTcRows = 16;
+constexpr int kTcRawStride = 40;
+
+template <typename T, int DV8, int HW>
+__global__ void __launch_bounds__(kTcWarps * 32)
+mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, const float* __restrict__ rot_tab) {
+  extern __shared__ __align__(16) unsigned char tc_smem[];
+  constexpr int HC = kTcWarps * HW;
+  constexpr int DVP = DV8 * 8;
+  const int row0 = tiles[3 * blockIdx.x], cnt = tiles[3 * blockIdx.x + 1], trow = tiles[3 * blockIdx.x + 2];
+  const int H = A.H, G = A.G, dk = A.dk, dv = A.dv, bs = A.block_size, rep = H / G;
+  const int h0 = blockIdx.y * HC;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, qr = lane >> 2, qc = (lane & 3) * 2;
+  const bool mixed = A.talk != nullptr;
+  const int g_lo = mixed ? 0 : h0 / rep;
+  const int Gs = (mixed ? G - 1 : min(H - 1, h0 + HC - 1) / rep) - g_lo + 1;   // kv heads staged per tile
+  const int ks = dk + 8, vs = DVP + 8;                                          // row strides in elements
+  const T* kp = static_cast<const T*>(A.k_pool);
+  const T* vp = static_cast<const T*>(A.v_pool);
+  const bool alias = (A.v_pool == A.k_pool) && dk == DVP;
+  T* Ks = reinterpret_cast<T*>(tc_smem);
+  T* Vs = alias ? Ks : Ks + Gs * kTcKeys * ks;
+  float* raw = reinterpret_cast<float*>(Vs + (alias ? Gs * kTcKeys * ks : Gs * kTcKeys * vs));   // [H][16][40]
+  float* talk_s = raw + (mixed ? H * kTcRows * kTcRawStride : 0);                               // [HC][H]
+  const int p0 = A.tok_pos[row0], p_last = p0 + cnt - 1;
+  const int32_t* table = A.block_tables + static_cast<int64_t>(trow) * A.table_stride;
+  const int lo0 = A.window > 0 ? max(0, p0 - A.window + 1) : 0;
+  const int kf = A.window > 0 ? min(A.keep_first, lo0) : 0;
+  const int nA = (kf + kTcKeys - 1) / kTcKeys;
+  const int cB0 = max(nA, lo0 / kTcKeys), cB1 = p_last / kTcKeys;
+  const int n_tiles = nA + (cB1 - cB0 + 1);
+  if (mixed)
+    for (int e = threadIdx.x; e < HC * H; e += blockDim.x) {
+      const int hl = e / H;
+      talk_s[e] = (h0 + hl < H) ? A.talk[(h0 + hl) * H + (e - hl * H)] : 0.f;
+    }
+  if (!alias && dv < DVP)     // value columns past dv are never staged: they stay zero
+    for (int e = threadIdx.x; e < Gs * kTcKeys * (DVP - dv); e += blockDim.x) {
+      const int r = e / (DVP - dv), c = e - r * (DVP - dv);
+      Vs[r * vs + dv + c] = Cvt<T>::from_f32(0.f);
+    }
+  float m_r[HW][2], l_r[HW][2], O[HW][DV8][4];
+#pragma unroll
+  for (int hw = 0; hw < HW; ++hw) {
+    m_r[hw][0] = m_r[hw][1] = -INFINITY;
+    l_r[hw][0] = l_r[hw][1] = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < DV8; ++nt) O[hw][nt][0] = O[hw][nt][1] = O[hw][nt][2] = O[hw][nt][3] = 0.f;
+  }
+  const T* qbase = static_cast<const T*>(A.q);
+  // S fragments of one head against the staged K tile; rows past the tile's tokens read zeros
+  auto scores = [&](int h, float (&s)[4][4]) {
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+    const T* qa = qbase + static_cast<int64_t>(row0 + qr) * A.q_tok_stride + h * A.q_head_stride + qc;
+    const T* qb = qa + 8 * A.q_tok_stride;
+    const bool va = qr < cnt, vb = qr + 8 < cnt;
+    const T* kt = Ks + (h / rep - g_lo) * kTcKeys * ks + qr * ks + qc;
+    for (int kk = 0; kk < dk; kk += 16) {
+      uint32_t a[4];
+      a[0] = va ? *reinterpret_cast<const uint32_t*>(qa + kk) : 0u;
+      a[1] = vb ? *reinterpret_cast<const uint32_t*>(qb + kk) : 0u;
+      a[2] = va ? *reinterpret_cast<const uint32_t*>(qa + kk + 8) : 0u;
+      a[3] = vb ? *reinterpret_cast<const uint32_t*>(qb + kk + 8) : 0u;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kt + nt * 8 * ks + kk);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kt + nt * 8 * ks + kk + 8);
+        Mma16x8<T>::mma(s[nt], a, b0, b1);
+      }
+    }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] *= A.scale;
+  };
+  for (int it = 0; it < n_tiles; ++it) {
+    const int j0 = (it < nA ? it : cB0 + it - nA) * kTcKeys;
+    __syncthreads();          // the previous tile has been consumed
+    {
+      const int kch = dk / 8;
+      for (int e = threadIdx.x; e < Gs * kTcKeys * kch; e += blockDim.x) {
+        const int ch = e % kch, r = e / kch, key = r % kTcKeys, gi = r / kTcKeys, j = j0 + key;
+        const bool ok = j <= p_last;
+        const T* src = ok ? kp + (static_cast<int64_t>(table[j / bs] * G + g_lo + gi) * bs + j % bs) * dk + ch * 8 : kp;
+        stage16(Ks + r * ks + ch * 8, src, ok);
+      }
+      if (!alias) {
+        const int vch = dv / 8;
+        for (int e = threadIdx.x; e < Gs * kTcKeys * vch; e += blockDim.x) {
+          const int ch = e % vch, r = e / vch, key = r % kTcKeys, gi = r / kTcKeys, j = j0 + key;
+          const bool ok = j <= p_last;
+          const T* src = ok ? vp + (static_cast<int64_t>(table[j / bs] * G + g_lo + gi) * bs + j % bs) * dv + ch * 8 : vp;
+          stage16(Vs + r * vs + ch * 8, src, ok);
+        }
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    if (mixed) {
+      for (int g = warp; g < H; g += kTcWarps) {
+        float s[4][4];
+        scores(g, s);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          float* dst = raw + (g * kTcRows + qr) * kTcRawStride + nt * 8 + qc;
+          dst[0] = s[nt][0];
+          dst[1] = s[nt][1];
+          dst[8 * kTcRawStride] = s[nt][2];
+          dst[8 * kTcRawStride + 1] = s[nt][3];
+        }
+      }
+      __syncthreads();
+    }
+#pragma unroll
+    for (int hw = 0; hw < HW; ++hw) {
+      const int hl = warp * HW + hw, h = h0 + hl;
+      if (h >= H) continue;      // uniform over the warp
+      float s[4][4];
+      if (mixed) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        for (int g = 0; g < H; ++g) {
+          const float tw = talk_s[hl * H + g];
+          const float* src = raw + (g * kTcRows + qr) * kTcRawStride + qc;
+#pragma unroll
+          for (int nt = 0; nt < 4; ++nt) {
+            s[nt][0] = fmaf(tw, src[nt * 8], s[nt][0]);
+            s[nt][1] = fmaf(tw, src[nt * 8 + 1], s[nt][1]);
+            s[nt][2] = fmaf(tw, src[8 * kTcRawStride + nt * 8], s[nt][2]);
+            s[nt][3] = fmaf(tw, src[8 * kTcRawStride + nt * 8 + 1], s[nt][3]);
+          }
+        }
+      } else {
+        scores(h, s);
+      }
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = qr + 8 * half, p = p0 + row;
+        const bool row_ok = row < cnt;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = j0 + nt * 8 + qc + e;
+            const bool ok = row_ok && j <= p && (A.window <= 0 || p - j < A.window || j < A.keep_first);
+            if (!ok) s[nt][2 * half + e] = -INFINITY;
+            mx = fmaxf(mx, s[nt][2 * half + e]);
+          }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_r[hw][half], mx);
+        float corr = 1.f, sum = 0.f;
+        if (m_new == -INFINITY) {        // nothing visible for this row yet: all weights are zero
+#pragma unroll
+          for (int nt = 0; nt < 4; ++nt) s[nt][2 * half] = s[nt][2 * half + 1] = 0.f;
+        } else {
+          corr = expf(m_r[hw][half] - m_new);
+#pragma unroll
+          for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const float w = expf(s[nt][2 * half + e] - m_new);   // exp(-inf) = 0 for hidden keys
+              s[nt][2 * half + e] = w;
+              sum += w;
+            }
+          m_r[hw][half] = m_new;
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l_r[hw][half] = l_r[hw][half] * corr + sum;
+#pragma unroll
+        for (int nt = 0; nt < DV8; ++nt) {
+          O[hw][nt][2 * half] *= corr;
+          O[hw][nt][2 * half + 1] *= corr;
+        }
+      }
+      const T* vt = Vs + ((h / rep - g_lo) * kTcKeys + (lane & 15)) * vs;
+#pragma unroll
+      for (int kst = 0; kst < 2; ++kst) {
+        uint32_t a[4];
+        a[0] = Mma16x8<T>::pack(s[2 * kst][0], s[2 * kst][1]);
+        a[1] = Mma16x8<T>::pack(s[2 * kst][2], s[2 * kst][3]);
+        a[2] = Mma16x8<T>::pack(s[2 * kst + 1][0], s[2 * kst + 1][1]);
+        a[3] = Mma16x8<T>::pack(s[2 * kst + 1][2], s[2 * kst + 1][3]);
+#pragma unroll
+        for (int nt = 0; nt < DV8; ++nt) {
+          uint32_t b0, b1;
+          const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(vt + kst * 16 * vs + nt * 8));
+          asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(b0), "=r"(b1) : "r"(addr));
+          Mma16x8<T>::mma(O[hw][nt], a, b0, b1);
+        }
+      }
+    }
+  }
+  __syncthreads();     // the staging area becomes the warps' output slabs
+  float* slab = reinterpret_cast<float*>(tc_smem) + warp * kTcRows * DVP;
+  T* outp = static_cast<T*>(A.out);
+  const T* gate = static_cast<const T*>(A.gate);
+#pragma unroll
+  for (int hw = 0; hw < HW; ++hw) {
+    const int h = h0 + warp * HW + hw;
+    if (h >= H) continue;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = qr + 8 * half;
+      float f = 0.f;
+      if (row < cnt) {
+        float m = m_r[hw][half], l = l_r[hw][half];
+        if (A.sink) {
+          const float sk = A.sink[h], M = fmaxf(m, sk);
+          l = l * expf(m - M) + expf(sk - M);
+          f = expf(m - M) / l;
+        } else {
+          f = 1.0f / l;
+        }
+        if (gate && !A.unrotate) f *= sigmoid_(Cvt<T>::to_f32(gate[static_cast<int64_t>(row0 + row) * A.gate_stride + h]));
+      }
+#pragma unroll
+      for (int nt = 0; nt < DV8; ++nt) {
+        O[hw][nt][2 * half] *= f;
+        O[hw][nt][2 * half + 1] *= f;
+      }
+    }
+    if (!A.unrotate) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = qr + 8 * half;
+        if (row >= cnt) continue;
+        T* orow = outp + static_cast<int64_t>(row0 + row) * A.out_tok_stride + h * A.out_head_stride;
+#pragma unroll
+        for (int nt = 0; nt < DV8; ++nt) {
+          const int c = nt * 8 + qc;
+          if (c < dv) *reinterpret_cast<uint32_t*>(orow + c) = Mma16x8<T>::pack(O[hw][nt][2 * half], O[hw][nt][2 * half + 1]);
+        }
+      }
+    } else {
+      __syncwarp();
+#pragma unroll
+      for (int nt = 0; nt < DV8; ++nt) {
+        slab[qr * DVP + nt * 8 + qc] = O[hw][nt][0];
+        slab[qr * DVP + nt * 8 + qc + 1] = O[hw][nt][1];
+        slab[(qr + 8) * DVP + nt * 8 + qc] = O[hw][nt][2];
+        slab[(qr + 8) * DVP + nt * 8 + qc + 1] = O[hw][nt][3];
+      }
+      __syncwarp();
+      const int vh = dv / 2;
+      for (int e = lane; e < cnt * vh; e += 32) {
+        const int row = e / vh, i = e - row * vh;
+        const float cf = rot_tab[(static_cast<int64_t>(row0 + row) * vh + i) * 2];
+        const float sf = rot_tab[(static_cast<int64_t>(row0 + row) * vh + i) * 2 + 1];
+        const int a = A.interleaved ? 2 * i : i, b = A.interleaved ? 2 * i + 1 : i + vh;
+        const float u = slab[row * DVP + a], w = slab[row * DVP + b];
+        float ya = u * cf + w * sf, yb = w * cf - u * sf;       // the rotation by minus the position
+        if (gate) {
+          const float gt = sigmoid_(Cvt<T>::to_f32(gate[static_cast<int64_t>(row0 + row) * A.gate_stride + h]));
+          ya *= gt;
+          yb *= gt;
+        }
+        T* orow = outp + static_cast<int64_t>(row0 + row) * A.out_tok_stride + h * A.out_head_stride;
+        orow[a] = Cvt<T>::from_f32(ya);
+        orow[b] = Cvt<T>::from_f32(yb);
+      }
+      if (dv & 1)
+        for (int row = lane; row < cnt; row += 32)
+          outp[static_cast<int64_t>(row0 + row) * A.out_tok_stride + h * A.out_head_stride + dv - 1] =
+              Cvt<T>::from_f32(slab[row * DVP + dv - 1]);
+    }
+  }
+}
+
+struct TcPlan {
+  int dv8, hw;
+  size_t smem;
+};
+
+inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool, bool unrotate, int dtype, TcPlan* plan) {
+  if (dtype == B200_DTYPE_F32 || dk % 16 || dv % 8 || dv > 256 || H % G) return false;
+  const int dv8 = dv <= 64 ? 8 : (dv <= 128 ? 16 : 32), dvp = dv8 * 8;
+  const int hw = (dv8 <= 16 && H > kTcWarps) ? 2 : 1;
+  const int gs = has_talk ? G : std::min(G, (kTcWarps * hw + H / G - 1) / (H / G) + 1);
+  const bool alias = same_pool && dk == dvp;
+  size_t bytes = static_cast<size_t>(gs) * kTcKeys * (dk + 8) * 2;
+  if (!alias) bytes += static_cast<size_t>(gs) * kTcKeys * (dvp + 8) * 2;
+  if (has_talk) bytes += sizeof(float) * (static_cast<size_t>(H) * kTcRows * kTcRawStride + static_cast<size_t>(kTcWarps) * hw * H);
+  if (unrotate) bytes = std::max(bytes, sizeof(float) * kTcWarps * kTcRows * static_cast<size_t>(dvp));
+  if (bytes > 227 * 1024) return false;
+  if (plan) *plan = TcPlan{dv8, hw, bytes};
+  return true;
+}
+
 // ---- short causal convolution + SiLU -----------------------------------------------------------------------------
 struct SeqSpan {
   int tok0;   // first packed row
@@ -700,7 +1048,7 @@ int b200_xielu(void* out, const void* z, int64_t z_stride, const void* pq, int r
 int b200_rotary_kv_append(void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
                           void* k_pool, void* v_pool, const int64_t* slot_mapping, const int32_t* tok_pos, int n_tok, int H,
                           int G, int dk, int dv, int rot_dims, float rot_base, int rotate_values, int interleaved,
-                          int block_size, int64_t max_blocks, int dtype, void* stream) {
+                          int block_size, int64_t max_blocks, float* value_rot, int dtype, void* stream) {
   if (n_tok < 0 || H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || block_size <= 0 || max_blocks <= 0)
     return fail(B200_EINVAL, "b200_rotary_kv_append: bad sizes");
   if (rot_dims < 0 || rot_dims > dk || (rot_dims & 1)) return fail(B200_ESHAPE, "b200_rotary_kv_append: rot_dims %d", rot_dims);
@@ -712,7 +1060,7 @@ int b200_rotary_kv_append(void* q, int64_t q_stride, const void* k, int64_t k_st
     rotary_kv_append_kernel<T><<<n_tok, 256, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<T*>(q), q_stride, static_cast<const T*>(k), k_stride, static_cast<const T*>(v), v_stride,
         static_cast<T*>(k_pool), static_cast<T*>(v_pool), slot_mapping, tok_pos, H, G, dk, dv, rot_dims,
-        static_cast<double>(rot_base), rotate_values, interleaved, block_size);
+        static_cast<double>(rot_base), rotate_values, interleaved, block_size, rotate_values ? value_rot : nullptr);
     return check_launch("b200_rotary_kv_append");
   });
 }
@@ -766,6 +1114,51 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
     else if (dvc == 8) launch(mixed_paged_attn_kernel<T, 4, 8>);
     else launch(mixed_paged_attn_kernel<T, 2, 16>);
     return check_launch("b200_mixed_paged_attn");
+  });
+}
+
+int b200_mixed_prompt_attn_supported(int H, int G, int dk, int dv, int has_talk, int same_pool, int unrotate, int dtype) {
+  if (H <= 0 || G <= 0) return 0;
+  return tc_plan(H, G, dk, dv, has_talk != 0, same_pool != 0, unrotate != 0, dtype, nullptr) ? 1 : 0;
+}
+
+int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q, int64_t q_tok_stride,
+                           int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
+                           const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tiles,
+                           int n_tiles, const int32_t* tok_pos, const float* talk, const float* sink, float scale,
+                           int window, int keep_first, const float* value_rot, int interleaved, int H, int G, int dk,
+                           int dv, int block_size, int dtype, void* stream) {
+  if (n_tiles < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0)
+    return fail(B200_EINVAL, "b200_mixed_prompt_attn: bad sizes");
+  if (n_tiles == 0) return 0;
+  if (!out || !q || !k_pool || !v_pool || !block_tables || !tiles || !tok_pos)
+    return fail(B200_EINVAL, "b200_mixed_prompt_attn: null pointer");
+  if ((q_tok_stride | q_head_stride | out_tok_stride | out_head_stride) & 1)
+    return fail(B200_ESHAPE, "b200_mixed_prompt_attn: odd strides");
+  TcPlan plan;
+  if (!tc_plan(H, G, dk, dv, talk != nullptr, k_pool == v_pool, value_rot != nullptr, dtype, &plan))
+    return fail(B200_ESHAPE, "b200_mixed_prompt_attn: sizes off the tensor-core grid (dk %d, dv %d)", dk, dv);
+  AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
+             block_tables, table_stride, nullptr, tok_pos, talk, sink, scale, window, keep_first, value_rot != nullptr,
+             interleaved, 0.0, H, G, dk, dv, block_size};
+  const dim3 grid(n_tiles, (H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw));
+  return hybrid_by_dtype(dtype, "b200_mixed_prompt_attn", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    if constexpr (std::is_same_v<T, float>) {
+      return fail(B200_ESHAPE, "b200_mixed_prompt_attn: 16-bit storage types only");
+    } else {
+      auto launch = [&](auto kern) {
+        if (plan.smem > 48 * 1024)
+          cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem));
+        kern<<<grid, kTcWarps * 32, plan.smem, static_cast<cudaStream_t>(stream)>>>(A, tiles, value_rot);
+      };
+      if (plan.dv8 == 8 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 8, 1>);
+      else if (plan.dv8 == 8) launch(mixed_prompt_attn_kernel<T, 8, 2>);
+      else if (plan.dv8 == 16 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 16, 1>);
+      else if (plan.dv8 == 16) launch(mixed_prompt_attn_kernel<T, 16, 2>);
+      else launch(mixed_prompt_attn_kernel<T, 32, 1>);
+      return check_launch("b200_mixed_prompt_attn");
+    }
   });
 }
 

@@ -351,9 +351,11 @@ def xielu(z: torch.Tensor, pq: torch.Tensor) -> torch.Tensor:
 @_timed
 def rotary_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                      slot_mapping: torch.Tensor, tok_pos: torch.Tensor, H: int, rot_dims: int, rot_base: float,
-                     rotate_values: bool, interleaved: bool = False) -> None:
+                     rotate_values: bool, interleaved: bool = False, want_table: bool = False) -> Optional[torch.Tensor]:
     """Rotary positions on q (in place) and k over their first ``rot_dims`` dimensions, optionally the values turned
-    over their whole width; k and v are stored in the pools at ``slot_mapping``."""
+    over their whole width; k and v are stored in the pools at ``slot_mapping``.  With ``want_table`` returns fp32
+    ``[n, dv // 2, 2]`` = (cos, sin) of the value pairs' angles (what ``mixed_prompt_attention`` turns outputs back
+    with)."""
     _need_cuda(q, k, v, k_pool, v_pool, slot_mapping, tok_pos)
     nb, G, bs, dk = k_pool.shape
     dv = v_pool.shape[3]
@@ -362,11 +364,14 @@ def rotary_kv_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, k_pool: 
         raise ValueError("q / k / v do not match the pools")
     if slot_mapping.dtype != torch.int64 or tok_pos.dtype != torch.int32:
         raise TypeError("slot_mapping is int64, tok_pos int32")
+    table = (torch.empty((n, dv // 2, 2), dtype=torch.float32, device=q.device)
+             if want_table and rotate_values else None)
     rc = _lib_().b200_rotary_kv_append(q.data_ptr(), _rows2(q), k.data_ptr(), _rows2(k), v.data_ptr(), _rows2(v),
                                        k_pool.data_ptr(), v_pool.data_ptr(), slot_mapping.data_ptr(), tok_pos.data_ptr(),
                                        n, H, G, dk, dv, int(rot_dims), float(rot_base), int(rotate_values),
-                                       int(interleaved), bs, nb, DTYPE_ID[k_pool.dtype], _stream())
+                                       int(interleaved), bs, nb, _ptr(table), DTYPE_ID[k_pool.dtype], _stream())
     _lib.check_mixers(rc, "b200_rotary_kv_append")
+    return table
 
 
 @_timed
@@ -416,6 +421,51 @@ def mixed_paged_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tens
                                        int(keep_first), int(unrotate_base is not None), int(interleaved),
                                        float(unrotate_base or 0.0), H, G, dk, dv, bs, DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_paged_attn")
+
+
+def mixed_prompt_attention_supported(H: int, G: int, dk: int, dv: int, has_talk: bool, same_pool: bool, unrotate: bool,
+                                     dtype: torch.dtype) -> bool:
+    return bool(_lib_().b200_mixed_prompt_attn_supported(int(H), int(G), int(dk), int(dv), int(has_talk), int(same_pool),
+                                                         int(unrotate), DTYPE_ID[dtype]))
+
+
+PROMPT_TILE_TOKENS = 16     # tokens of one sequence a CTA of ``mixed_prompt_attention`` serves
+
+
+@_timed
+def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                           block_tables: torch.Tensor, tiles: torch.Tensor, tok_pos: torch.Tensor, scale: float,
+                           talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
+                           keep_first: int = 0, value_rot: Optional[torch.Tensor] = None, interleaved: bool = False,
+                           gate: Optional[torch.Tensor] = None) -> None:
+    """``mixed_paged_attention`` on the tensor cores for prompt portions and decoded tokens alike (16-bit dtypes, see
+    ``mixed_prompt_attention_supported``).  ``tiles`` int32 ``[n_tiles, 3]``: up to ``PROMPT_TILE_TOKENS`` consecutive
+    tokens of one sequence each; ``value_rot``: the table ``rotary_kv_append`` returned for this step's tokens."""
+    _need_cuda(out, q, k_pool, v_pool, block_tables, tiles, tok_pos)
+    nb, G, bs, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    n, H = q.shape[0], q.shape[1]
+    if q.dim() != 3 or q.shape[2] != dk or tuple(out.shape) != (n, H, dv) or q.stride(2) != 1 or out.stride(2) != 1:
+        raise ValueError("q must be [n, H, dk] and out [n, H, dv] with contiguous last dimensions")
+    if out.dtype != q.dtype or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+        raise TypeError("q, out and the pools share one dtype")
+    if tiles.dtype != torch.int32 or tiles.dim() != 2 or tiles.shape[1] != 3 or not tiles.is_contiguous():
+        raise ValueError("tiles must be contiguous int32 [n_tiles, 3]")
+    for t, shape in ((talk, (H, H)), (sink, (H,))):
+        if t is not None and (t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous()):
+            raise ValueError("talk is contiguous fp32 [H, H], sink fp32 [H]")
+    if value_rot is not None and (tuple(value_rot.shape) != (n, dv // 2, 2) or value_rot.dtype != torch.float32
+                                  or not value_rot.is_contiguous()):
+        raise ValueError("value_rot must be contiguous fp32 [n, dv // 2, 2]")
+    if gate is not None and (tuple(gate.shape) != (n, H) or gate.dtype != q.dtype):
+        raise ValueError("gate must be [n, H] in the activations' dtype")
+    rc = _lib_().b200_mixed_prompt_attn(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
+                                        _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
+                                        v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(),
+                                        tiles.shape[0], tok_pos.data_ptr(), _ptr(talk), _ptr(sink), float(scale), int(window),
+                                        int(keep_first), _ptr(value_rot), int(interleaved), H, G, dk, dv, bs,
+                                        DTYPE_ID[q.dtype], _stream())
+    _lib.check_mixers(rc, "b200_mixed_prompt_attn")
 
 
 @_timed

@@ -151,6 +151,8 @@ class WindowedSinkAttention(nn.Module):
         self.w_o = _param(t["o"], device, dtype)
         self.talk = _param(t["talk"], device, torch.float32) if "talk" in t else None
         self.sink = _param(t["sink"], device, torch.float32) if "sink" in t else None
+        self.tensor_cores = mixer_ops.mixed_prompt_attention_supported(
+            self.H, self.G, self.dk, self.dv, self.talk is not None, False, self.rotate_values, self.w_in.dtype)
 
     def forward(self, h: torch.Tensor, cache: RaggedLayerCache) -> torch.Tensor:
         st, n = cache.state, h.shape[0]
@@ -158,14 +160,22 @@ class WindowedSinkAttention(nn.Module):
         proj = F.linear(h, self.w_in, self.b_in)
         c = self.cuts
         q, k, v = proj[:, c[0]:c[0] + H * dk], proj[:, c[1]:c[1] + G * dk], proj[:, c[2]:c[2] + G * dv]
-        mixer_ops.rotary_kv_append(q, k, v, cache.k_pool, cache.v_pool, st.slot_mapping, st.tok_pos, H, self.rot_dims,
-                                   self.rot_base, self.rotate_values, self.interleaved)
+        table = mixer_ops.rotary_kv_append(q, k, v, cache.k_pool, cache.v_pool, st.slot_mapping, st.tok_pos, H,
+                                           self.rot_dims, self.rot_base, self.rotate_values, self.interleaved,
+                                           want_table=self.tensor_cores)
         attn = torch.empty((n, H, dv), dtype=h.dtype, device=h.device)
-        mixer_ops.mixed_paged_attention(attn, q.unflatten(1, (H, dk)), cache.k_pool, cache.v_pool, st.block_tables,
-                                        st.tok_row, st.tok_pos, self.scale, talk=self.talk, sink=self.sink,
-                                        window=self.window, keep_first=self.keep_first,
-                                        unrotate_base=self.rot_base if self.rotate_values else None,
-                                        interleaved=self.interleaved)
+        if self.tensor_cores:     # 16-bit storage and sizes the tensor-core kernel takes: portions and single tokens
+            tiles, _ = st.prompt_tiles(1, mixer_ops.PROMPT_TILE_TOKENS)
+            mixer_ops.mixed_prompt_attention(attn, q.unflatten(1, (H, dk)), cache.k_pool, cache.v_pool, st.block_tables,
+                                             tiles, st.tok_pos, self.scale, talk=self.talk, sink=self.sink,
+                                             window=self.window, keep_first=self.keep_first, value_rot=table,
+                                             interleaved=self.interleaved)
+        else:                     # fp32, or head sizes off the tensor-core grid: the row kernel
+            mixer_ops.mixed_paged_attention(attn, q.unflatten(1, (H, dk)), cache.k_pool, cache.v_pool, st.block_tables,
+                                            st.tok_row, st.tok_pos, self.scale, talk=self.talk, sink=self.sink,
+                                            window=self.window, keep_first=self.keep_first,
+                                            unrotate_base=self.rot_base if self.rotate_values else None,
+                                            interleaved=self.interleaved)
         return F.linear(attn.view(n, H * dv), self.w_o)
 
 
@@ -190,6 +200,8 @@ class LatentAttention(nn.Module):
         self.w_uk = _param(t["uk"].reshape(self.H, self.dk, self.rank), device, dtype)                  # [H, dk, r]
         self.w_uv = _param(t["uv"].reshape(self.H, self.dv, self.rank).transpose(1, 2), device, dtype)  # [H, r, dv]
         self.w_o = _param(t["o"], device, dtype)
+        self.tensor_cores = mixer_ops.mixed_prompt_attention_supported(self.H, 1, self.rank, self.rank, False, True,
+                                                                       False, self.w_in.dtype)
 
     def forward(self, h: torch.Tensor, cache: RaggedLayerCache) -> torch.Tensor:
         st, n = cache.state, h.shape[0]
@@ -200,9 +212,14 @@ class LatentAttention(nn.Module):
         q = F.linear(cq, self.w_uq).view(n, H, self.dk)
         q_lat = torch.bmm(q.transpose(0, 1), self.w_uk)                          # [H, n, r]
         o_lat = torch.empty((H, n, r), dtype=h.dtype, device=h.device)
-        mixer_ops.mixed_paged_attention(o_lat.transpose(0, 1), q_lat.transpose(0, 1), cache.k_pool, cache.k_pool,
-                                        st.block_tables, st.tok_row, st.tok_pos, self.scale,
-                                        gate=proj[:, c[2]:c[2] + H])
+        if self.tensor_cores:
+            tiles, _ = st.prompt_tiles(1, mixer_ops.PROMPT_TILE_TOKENS)
+            mixer_ops.mixed_prompt_attention(o_lat.transpose(0, 1), q_lat.transpose(0, 1), cache.k_pool, cache.k_pool,
+                                             st.block_tables, tiles, st.tok_pos, self.scale, gate=proj[:, c[2]:c[2] + H])
+        else:
+            mixer_ops.mixed_paged_attention(o_lat.transpose(0, 1), q_lat.transpose(0, 1), cache.k_pool, cache.k_pool,
+                                            st.block_tables, st.tok_row, st.tok_pos, self.scale,
+                                            gate=proj[:, c[2]:c[2] + H])
         o = torch.bmm(o_lat, self.w_uv)                                          # [H, n, dv]
         return F.linear(o.transpose(0, 1).reshape(n, H * self.dv), self.w_o)
 

@@ -131,11 +131,12 @@ int b200_xielu(void* out, const void* z, int64_t z_stride, const void* pq, int r
 /* Rotary positions on the first rot_dims dimensions of every q head (in place) and k head, pair (i, i + rot_dims/2)
  * (interleaved: (2i, 2i + 1)) turned by pos * rot_base^(-2i / rot_dims); with rotate_values, the values are turned the
  * same way over their whole width dv by pos * rot_base^(-2m / dv).  k and v go to the pools ([max_blocks, G, block_size,
- * dk | dv]) at slot_mapping (negative = skip).  Angles are formed in double precision. */
+ * dk | dv]) at slot_mapping (negative = skip).  Angles are formed in double precision.  value_rot (may be NULL): fp32
+ * [n_tok, dv / 2, 2] receives (cos, sin) of every value pair's angle, for the attention kernel that turns outputs back. */
 int b200_rotary_kv_append(void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
                           void* k_pool, void* v_pool, const int64_t* slot_mapping, const int32_t* tok_pos, int n_tok, int H,
                           int G, int dk, int dv, int rot_dims, float rot_base, int rotate_values, int interleaved,
-                          int block_size, int64_t max_blocks, int dtype, void* stream);
+                          int block_size, int64_t max_blocks, float* value_rot, int dtype, void* stream);
 
 /* pool[slot] = rms_norm(x[n]; weight): latent rows of `width` into a one-head pool [max_blocks, 1, block_size, width]. */
 int b200_norm_append(const void* x, int64_t x_stride, const void* weight, float weight_offset, float eps, void* pool,
@@ -155,6 +156,19 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
                           const int32_t* tok_pos, int n_tok, const float* talk, const float* sink, float scale, int window,
                           int keep_first, int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv,
                           int block_size, int dtype, void* stream);
+
+/* The same attention on the tensor cores (16-bit T; dk a multiple of 16, dv a multiple of 8 up to 256, and a shared-
+ * memory budget that b200_mixed_prompt_attn_supported checks; same_pool: keys and values are one pool).  tiles: int32
+ * [n_tiles, 3] = (first packed row, token count <= 16, block-table row); a tile's tokens are consecutive positions of
+ * one sequence.  Outputs are turned back when value_rot (the table b200_rotary_kv_append wrote for these tokens) is
+ * given.  Scores, mask and softmax are fp32; the weights are rounded to T only as the operand of the P.V product. */
+int b200_mixed_prompt_attn_supported(int H, int G, int dk, int dv, int has_talk, int same_pool, int unrotate, int dtype);
+int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q, int64_t q_tok_stride,
+                           int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
+                           const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tiles,
+                           int n_tiles, const int32_t* tok_pos, const float* talk, const float* sink, float scale,
+                           int window, int keep_first, const float* value_rot, int interleaved, int H, int G, int dk,
+                           int dv, int block_size, int dtype, void* stream);
 
 /* out[t, c] = silu(sum_i w[c][i] * x[t - (taps - 1 - i), c]) per sequence (SeqSpan rows); inputs before the portion
  * come from tail [slots, taps - 1, C] (fp32, oldest first), which then receives the portion's last taps - 1 inputs. */

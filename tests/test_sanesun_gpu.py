@@ -64,6 +64,19 @@ CFG_B = {  # other order; ten heads (two passes of the attention kernel) mixed b
 }
 
 
+CFG_C = {  # sizes the tensor-core attention takes in 16-bit storage: a value width below its tile (48 of 64) that is
+           # turned back, twelve mixed heads over four kv heads, a latent whose one pool serves both products
+    "architecture": "Sanesun", "width": 64, "vocab": 41, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6},
+    "layers": [
+        with_mlp(attn(4, 2, 32, 48, 19, 3, 16, base=200.0), 48),
+        with_mlp(latent(10, 16, 24, 64, 40), 32),
+        with_mlp(delta(2, 1, 32, 32, 3), None),
+        with_mlp(attn(12, 4, 16, 128, 40, 0, 16), 32),
+        with_mlp(latent(3, 8, 8, 80, 24), None),
+    ],
+}
+
+
 def build(cfg_raw, dtype=torch.float32, seed=0, max_tokens=512, max_seqs=4):
     from dgi_b200 import sanesun_layer as S
     from dgi_b200.ragged_engine import RaggedStepEngine
@@ -215,6 +228,84 @@ def test_attention_finds_one_far_key_among_hundreds():
     assert w[far] > 0.9                                        # the far key really carries the answer
 
 
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
+@pytest.mark.parametrize("H,G,dk,dv,mixing", [(4, 2, 32, 48, True), (12, 4, 16, 128, True), (20, 20, 16, 64, True),
+                                              (3, 1, 64, 64, False), (10, 2, 48, 256, False)])
+def test_tensor_core_attention_matches_the_statement(dt, H, G, dk, dv, mixing):
+    """The 16-bit kernel for portions and single tokens: window and prefix edges inside one 16-token tile, tiles that
+    straddle pages and key tiles, a needle just inside and just outside, turned-back outputs, gates."""
+    from dgi_b200 import mixer_ops as M
+
+    g = torch.Generator().manual_seed(8)
+    n, size, keep, base = 200, 37, 5, 90.0
+    q, k, v = (torch.randn(n, x, d, generator=g).to(dt) for x, d in ((H, dk), (G, dk), (G, dv)))
+    i = 170
+    for j in (i - size + 1, i - size):          # seen / hidden needle for head 0's group
+        k[j, 0] = (5.0 * q[i, 0].float() / q[i, 0].float().norm()).to(dt)
+    talk = (torch.eye(H) + 0.3 * torch.randn(H, H, generator=g) / math.sqrt(H)) if mixing else None
+    sink = torch.randn(H, generator=g) if mixing else None
+    gate = None if mixing else torch.randn(n, H, generator=g).to(dt)
+    assert M.mixed_prompt_attention_supported(H, G, dk, dv, mixing, False, mixing, dt)
+    pos = torch.arange(n)
+    vt = R.turn(v.to(F64), pos, dv, base).to(dt) if mixing else v            # stored turned, as the append leaves them
+    kp, vp, table = paged(k, vt)
+    tab = None
+    if mixing:
+        ang = pos.to(F64)[:, None] * base ** (-2.0 * torch.arange(dv // 2, dtype=F64) / dv)
+        tab = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).float().to(DEV)
+    # tiles: whole 16-token runs from 0, a run cut at an odd place, single tokens at the end
+    cuts = [16] * 5 + [3, 13, 16, 16, 16, 16, 7, 9] + [1] * 24
+    assert sum(cuts) == n
+    tiles, at = [], 0
+    for c in cuts:
+        tiles.append((at, c, 0))
+        at += c
+    out = torch.full((n, H, dv), float("nan"), dtype=dt, device=DEV)
+    M.mixed_prompt_attention(out, q.to(DEV), kp, vp, table, torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                             pos.to(torch.int32).to(DEV), 0.3, talk=None if talk is None else talk.to(DEV),
+                             sink=None if sink is None else sink.to(DEV), window=size, keep_first=keep, value_rot=tab,
+                             gate=None if gate is None else gate.to(DEV))
+    rows = [0, 1, keep, 15, 16, 17, size - 1, size, size + keep, 95, 96, 97, i, n - 25, n - 24, n - 1]
+    ref = R.windowed_attention(q.to(F64), k.to(F64), vt.to(F64), 0.3, size, keep, None if talk is None else talk.to(F64),
+                               None if sink is None else sink.to(F64), rows=rows)
+    if mixing:
+        ref = R.turn(ref, pos, dv, base, back=True)
+    else:
+        ref = ref * torch.sigmoid(gate.to(F64))[:, :, None]
+    got = out.cpu().to(F64)
+    assert torch.isfinite(got).all()
+    err = (got[rows] - ref[rows]).abs().max().item()
+    assert err <= 2e-2 * max(1.0, ref[rows].abs().max().item()), err
+    # the row kernel is the fp32 / odd-size fallback of the same contract: both agree on every row
+    out2 = torch.empty_like(out)
+    M.mixed_paged_attention(out2, q.to(DEV), kp, vp, table, torch.zeros(n, dtype=torch.int32, device=DEV),
+                            pos.to(torch.int32).to(DEV), 0.3, talk=None if talk is None else talk.to(DEV),
+                            sink=None if sink is None else sink.to(DEV), window=size, keep_first=keep,
+                            unrotate_base=base if mixing else None, gate=None if gate is None else gate.to(DEV))
+    assert (out2.float() - out.float()).abs().max().item() <= 2e-2 * max(1.0, ref[rows].abs().max().item())
+
+
+def test_tensor_core_latent_attention_reads_one_pool_for_keys_and_values():
+    from dgi_b200 import mixer_ops as M
+
+    g = torch.Generator().manual_seed(9)
+    n, H, r = 300, 5, 128
+    q, c = torch.randn(n, H, r, generator=g).bfloat16(), torch.randn(n, 1, r, generator=g).bfloat16()
+    far, i = 21, n - 1
+    c[far, 0] = (9.0 * q[i, 2].float() / q[i, 2].float().norm()).bfloat16()
+    kp, _, table = paged(c, c)
+    tiles = torch.tensor([(lo, min(16, n - lo), 0) for lo in range(0, n, 16)], dtype=torch.int32, device=DEV)
+    out = torch.empty((H, n, r), dtype=torch.bfloat16, device=DEV)            # head-major, as the latent mixer has it
+    M.mixed_prompt_attention(out.transpose(0, 1), q.to(DEV), kp, kp, table, tiles,
+                             torch.arange(n, dtype=torch.int32, device=DEV), 0.09)
+    rows = [0, 15, 16, far, 150, i]
+    ref = R.windowed_attention(q.to(F64), c.to(F64), c.to(F64), 0.09, rows=rows)
+    got = out.transpose(0, 1).cpu().to(F64)
+    assert (got[rows] - ref[rows]).abs().max().item() <= 2e-2 * ref[rows].abs().max().item()
+    w = torch.softmax((c[: i + 1, 0].to(F64) @ q[i, 2].to(F64)) * 0.09, 0)
+    assert w[far] > 0.9
+
+
 def test_value_rotation_cancels_to_the_distance():
     """Values stored turned by j and read back turned by -i: a lone visible key returns its value turned by j - i."""
     from dgi_b200 import mixer_ops as M
@@ -282,7 +373,7 @@ def test_delta_rule_state_through_portions(H, G, dk, dv):
 
 # ---- whole models ----------------------------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("cfg", [CFG_A, CFG_B], ids=["A", "B"])
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_B, CFG_C], ids=["A", "B", "C"])
 def test_whole_prompt_fp32(cfg):
     engine, tensors = build(cfg)
     toks = tokens(90, cfg["vocab"], 11)
@@ -291,7 +382,7 @@ def test_whole_prompt_fp32(cfg):
     close(whole(engine, "b", one), R.forward(cfg, tensors, one), 3e-5)
 
 
-@pytest.mark.parametrize("cfg", [CFG_A, CFG_B], ids=["A", "B"])
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_B, CFG_C], ids=["A", "B", "C"])
 def test_whole_prompt_bf16(cfg):
     engine, tensors = build(cfg, dtype=torch.bfloat16)
     toks = tokens(70, cfg["vocab"], 13)
@@ -362,8 +453,8 @@ def test_mixed_batches_match_each_request_alone_and_reuse_pages_and_slots():
     assert engine.free_slots == 3 and engine.free_blocks == 256 // 16
 
 
-def test_logits_do_not_depend_on_the_batch_or_the_cut_beyond_rounding_bf16():
-    cfg = CFG_A
+@pytest.mark.parametrize("cfg", [CFG_A, CFG_C], ids=["A", "C"])
+def test_logits_do_not_depend_on_the_batch_or_the_cut_beyond_rounding_bf16(cfg):
     engine, _ = build(cfg, dtype=torch.bfloat16)
     a, b = tokens(80, cfg["vocab"], 31), tokens(37, cfg["vocab"], 32)
     alone = whole(engine, "a", a)
