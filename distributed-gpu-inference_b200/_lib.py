@@ -145,10 +145,12 @@ MIXER_SIGNATURES = {
                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_float, c_int,
                 c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_mixed_prompt_attn_supported": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "b200_mixed_prompt_attn_splits": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "b200_mixed_prompt_attn_workspace": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200_mixed_prompt_attn": (
         c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_int, c_int,
-                c_int, c_int, c_int, c_int, c_void_p]),
+                c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_int,
+                c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "b200_causal_conv_silu": (
         c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                 c_void_p]),

@@ -303,7 +303,7 @@ def _sanesun_kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> D
         by: Dict[str, List[float]] = {}
         seen_attn = 0
         for name, a, b in events:
-            if name == "mixed_paged_attention":
+            if name in ("mixed_paged_attention", "mixed_prompt_attention"):
                 name = ("windowed_attention", "latent_attention")[seen_attn % 2]
                 seen_attn += 1
             by.setdefault(name, []).append(a.elapsed_time(b) * 1e-3)

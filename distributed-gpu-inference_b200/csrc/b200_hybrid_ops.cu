@@ -489,7 +489,8 @@ constexpr int kTcRawStride = 40;
 
 template <typename T, int DV8, int HW>
 __global__ void __launch_bounds__(kTcWarps * 32)
-mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, const float* __restrict__ rot_tab) {
+mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, const float* __restrict__ rot_tab,
+                         float* __restrict__ ws, int n_tok, int stages) {
   extern __shared__ __align__(16) unsigned char tc_smem[];
   constexpr int HC = kTcWarps * HW;
   constexpr int DVP = DV8 * 8;
@@ -504,9 +505,11 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
   const T* kp = static_cast<const T*>(A.k_pool);
   const T* vp = static_cast<const T*>(A.v_pool);
   const bool alias = (A.v_pool == A.k_pool) && dk == DVP;
-  T* Ks = reinterpret_cast<T*>(tc_smem);
-  T* Vs = alias ? Ks : Ks + Gs * kTcKeys * ks;
-  float* raw = reinterpret_cast<float*>(Vs + (alias ? Gs * kTcKeys * ks : Gs * kTcKeys * vs));   // [H][16][40]
+  const int stage_elems = Gs * kTcKeys * (ks + (alias ? 0 : vs));                 // one stage: K rows, then V rows
+  T* stage0 = reinterpret_cast<T*>(tc_smem);
+  const T* Ks = stage0;                                                         // the stage being computed on
+  const T* Vs = alias ? stage0 : stage0 + Gs * kTcKeys * ks;
+  float* raw = reinterpret_cast<float*>(stage0 + stages * stage_elems);         // [H][16][40]
   float* talk_s = raw + (mixed ? H * kTcRows * kTcRawStride : 0);                               // [HC][H]
   const int p0 = A.tok_pos[row0], p_last = p0 + cnt - 1;
   const int32_t* table = A.block_tables + static_cast<int64_t>(trow) * A.table_stride;
@@ -521,9 +524,10 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
       talk_s[e] = (h0 + hl < H) ? A.talk[(h0 + hl) * H + (e - hl * H)] : 0.f;
     }
   if (!alias && dv < DVP)     // value columns past dv are never staged: they stay zero
-    for (int e = threadIdx.x; e < Gs * kTcKeys * (DVP - dv); e += blockDim.x) {
-      const int r = e / (DVP - dv), c = e - r * (DVP - dv);
-      Vs[r * vs + dv + c] = Cvt<T>::from_f32(0.f);
+    for (int e = threadIdx.x; e < stages * Gs * kTcKeys * (DVP - dv); e += blockDim.x) {
+      const int sgi = e / (Gs * kTcKeys * (DVP - dv)), e2 = e - sgi * (Gs * kTcKeys * (DVP - dv));
+      const int r = e2 / (DVP - dv), c = e2 - r * (DVP - dv);
+      stage0[sgi * stage_elems + Gs * kTcKeys * ks + r * vs + dv + c] = Cvt<T>::from_f32(0.f);
     }
   float m_r[HW][2], l_r[HW][2], O[HW][DV8][4];
 #pragma unroll
@@ -560,30 +564,46 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
 #pragma unroll
       for (int e = 0; e < 4; ++e) s[nt][e] *= A.scale;
   };
-  for (int it = 0; it < n_tiles; ++it) {
+  // the K and V rows of key tile `it` into stage `b` (cp.async; rows past the sequence's end are zero-filled)
+  auto issue = [&](int it, int b) {
     const int j0 = (it < nA ? it : cB0 + it - nA) * kTcKeys;
-    __syncthreads();          // the previous tile has been consumed
-    {
-      const int kch = dk / 8;
-      for (int e = threadIdx.x; e < Gs * kTcKeys * kch; e += blockDim.x) {
-        const int ch = e % kch, r = e / kch, key = r % kTcKeys, gi = r / kTcKeys, j = j0 + key;
+    T* Kd = stage0 + b * stage_elems;
+    T* Vd = Kd + Gs * kTcKeys * ks;
+    const int kch = dk / 8;
+    for (int e = threadIdx.x; e < Gs * kTcKeys * kch; e += blockDim.x) {
+      const int ch = e % kch, r = e / kch, key = r % kTcKeys, gi = r / kTcKeys, j = j0 + key;
+      const bool ok = j <= p_last;
+      const T* src = ok ? kp + (static_cast<int64_t>(table[j / bs] * G + g_lo + gi) * bs + j % bs) * dk + ch * 8 : kp;
+      stage16(Kd + r * ks + ch * 8, src, ok);
+    }
+    if (!alias) {
+      const int vch = dv / 8;
+      for (int e = threadIdx.x; e < Gs * kTcKeys * vch; e += blockDim.x) {
+        const int ch = e % vch, r = e / vch, key = r % kTcKeys, gi = r / kTcKeys, j = j0 + key;
         const bool ok = j <= p_last;
-        const T* src = ok ? kp + (static_cast<int64_t>(table[j / bs] * G + g_lo + gi) * bs + j % bs) * dk + ch * 8 : kp;
-        stage16(Ks + r * ks + ch * 8, src, ok);
+        const T* src = ok ? vp + (static_cast<int64_t>(table[j / bs] * G + g_lo + gi) * bs + j % bs) * dv + ch * 8 : vp;
+        stage16(Vd + r * vs + ch * 8, src, ok);
       }
-      if (!alias) {
-        const int vch = dv / 8;
-        for (int e = threadIdx.x; e < Gs * kTcKeys * vch; e += blockDim.x) {
-          const int ch = e % vch, r = e / vch, key = r % kTcKeys, gi = r / kTcKeys, j = j0 + key;
-          const bool ok = j <= p_last;
-          const T* src = ok ? vp + (static_cast<int64_t>(table[j / bs] * G + g_lo + gi) * bs + j % bs) * dv + ch * 8 : vp;
-          stage16(Vs + r * vs + ch * 8, src, ok);
-        }
-      }
-      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // this CTA's share of the key tiles (gridDim.z > 1: steps of few tokens split the keys over CTAs)
+  const int per_split = (n_tiles + gridDim.z - 1) / gridDim.z;
+  const int it_lo = blockIdx.z * per_split, it_hi = min(n_tiles, it_lo + per_split);
+  __syncthreads();
+  if (it_lo < it_hi) issue(it_lo, 0);
+  for (int it = it_lo; it < it_hi; ++it) {
+    const int j0 = (it < nA ? it : cB0 + it - nA) * kTcKeys;
+    const int b = stages == 2 ? ((it - it_lo) & 1) : 0;
+    if (stages == 2 && it + 1 < it_hi) {
+      issue(it + 1, b ^ 1);       // that stage was last read one iteration ago, before the barrier that ended it
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
+    Ks = stage0 + b * stage_elems;
+    Vs = alias ? Ks : Ks + Gs * kTcKeys * ks;
     if (mixed) {
       for (int g = warp; g < H; g += kTcWarps) {
         float s[4][4];
@@ -591,10 +611,8 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt) {
           float* dst = raw + (g * kTcRows + qr) * kTcRawStride + nt * 8 + qc;
-          dst[0] = s[nt][0];
-          dst[1] = s[nt][1];
-          dst[8 * kTcRawStride] = s[nt][2];
-          dst[8 * kTcRawStride + 1] = s[nt][3];
+          *reinterpret_cast<float2*>(dst) = make_float2(s[nt][0], s[nt][1]);
+          *reinterpret_cast<float2*>(dst + 8 * kTcRawStride) = make_float2(s[nt][2], s[nt][3]);
         }
       }
       __syncthreads();
@@ -612,10 +630,12 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
           const float* src = raw + (g * kTcRows + qr) * kTcRawStride + qc;
 #pragma unroll
           for (int nt = 0; nt < 4; ++nt) {
-            s[nt][0] = fmaf(tw, src[nt * 8], s[nt][0]);
-            s[nt][1] = fmaf(tw, src[nt * 8 + 1], s[nt][1]);
-            s[nt][2] = fmaf(tw, src[8 * kTcRawStride + nt * 8], s[nt][2]);
-            s[nt][3] = fmaf(tw, src[8 * kTcRawStride + nt * 8 + 1], s[nt][3]);
+            const float2 lo = *reinterpret_cast<const float2*>(src + nt * 8);
+            const float2 hi = *reinterpret_cast<const float2*>(src + 8 * kTcRawStride + nt * 8);
+            s[nt][0] = fmaf(tw, lo.x, s[nt][0]);
+            s[nt][1] = fmaf(tw, lo.y, s[nt][1]);
+            s[nt][2] = fmaf(tw, hi.x, s[nt][2]);
+            s[nt][3] = fmaf(tw, hi.y, s[nt][3]);
           }
         }
       } else {
@@ -680,6 +700,30 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
         }
       }
     }
+    __syncthreads();          // the tile (and the raw scores) have been consumed
+    if (stages == 1 && it + 1 < it_hi) issue(it + 1, 0);
+  }
+  if (gridDim.z > 1) {
+    // partial (max, sum, unnormalised output) of this CTA's keys; the combine kernel merges the splits
+#pragma unroll
+    for (int hw = 0; hw < HW; ++hw) {
+      const int h = h0 + warp * HW + hw;
+      if (h >= H) continue;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = qr + 8 * half;
+        if (row >= cnt) continue;
+        float* dst = ws + ((static_cast<int64_t>(blockIdx.z) * n_tok + row0 + row) * H + h) * (DVP + 2);
+        if (qc == 0) {
+          dst[0] = m_r[hw][half];
+          dst[1] = l_r[hw][half];
+        }
+#pragma unroll
+        for (int nt = 0; nt < DV8; ++nt)
+          *reinterpret_cast<float2*>(dst + 2 + nt * 8 + qc) = make_float2(O[hw][nt][2 * half], O[hw][nt][2 * half + 1]);
+      }
+    }
+    return;
   }
   __syncthreads();     // the staging area becomes the warps' output slabs
   float* slab = reinterpret_cast<float*>(tc_smem) + warp * kTcRows * DVP;
@@ -757,8 +801,61 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
   }
 }
 
+// Merge of the key splits: one CTA per token.  out(h) = sum_s O_s e^(m_s - M) / (sum_s l_s e^(m_s - M) + e^(sink - M)),
+// then the turn back and the gate, as in the single-CTA epilogue.
+template <typename T>
+__global__ void __launch_bounds__(256)
+attn_split_combine_kernel(const AttnArgs A, const float* __restrict__ ws, int n_splits, int n_tok, int dvp,
+                          const float* __restrict__ rot_tab) {
+  extern __shared__ float res[];   // [H][dv]
+  const int n = blockIdx.x, H = A.H, dv = A.dv, stride = dvp + 2;
+  for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
+    const int h = e / dv, c = e - h * dv;
+    float M = A.sink ? A.sink[h] : -INFINITY;
+    for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, ws[((static_cast<int64_t>(sp) * n_tok + n) * H + h) * stride]);
+    float L = A.sink ? expf(A.sink[h] - M) : 0.f, O = 0.f;
+    for (int sp = 0; sp < n_splits; ++sp) {
+      const float* src = ws + ((static_cast<int64_t>(sp) * n_tok + n) * H + h) * stride;
+      const float f = src[0] == -INFINITY ? 0.f : expf(src[0] - M);
+      L = fmaf(src[1], f, L);
+      O = fmaf(src[2 + c], f, O);
+    }
+    res[e] = O / L;
+  }
+  __syncthreads();
+  T* out = static_cast<T*>(A.out) + static_cast<int64_t>(n) * A.out_tok_stride;
+  const T* gate = static_cast<const T*>(A.gate);
+  if (A.unrotate) {
+    const int vh = dv / 2;
+    for (int e = threadIdx.x; e < H * vh; e += blockDim.x) {
+      const int h = e / vh, i = e - h * vh;
+      const float cf = rot_tab[(static_cast<int64_t>(n) * vh + i) * 2], sf = rot_tab[(static_cast<int64_t>(n) * vh + i) * 2 + 1];
+      const int a = A.interleaved ? 2 * i : i, b = A.interleaved ? 2 * i + 1 : i + vh;
+      const float u = res[h * dv + a], w = res[h * dv + b];
+      float ya = u * cf + w * sf, yb = w * cf - u * sf;
+      if (gate) {
+        const float gt = sigmoid_(Cvt<T>::to_f32(gate[static_cast<int64_t>(n) * A.gate_stride + h]));
+        ya *= gt;
+        yb *= gt;
+      }
+      out[h * A.out_head_stride + a] = Cvt<T>::from_f32(ya);
+      out[h * A.out_head_stride + b] = Cvt<T>::from_f32(yb);
+    }
+    if (dv & 1)
+      for (int h = threadIdx.x; h < H; h += blockDim.x)
+        out[h * A.out_head_stride + dv - 1] = Cvt<T>::from_f32(res[h * dv + dv - 1]);
+  } else {
+    for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
+      const int h = e / dv, c = e - h * dv;
+      float y = res[e];
+      if (gate) y *= sigmoid_(Cvt<T>::to_f32(gate[static_cast<int64_t>(n) * A.gate_stride + h]));
+      out[h * A.out_head_stride + c] = Cvt<T>::from_f32(y);
+    }
+  }
+}
+
 struct TcPlan {
-  int dv8, hw;
+  int dv8, hw, stages;
   size_t smem;
 };
 
@@ -768,12 +865,17 @@ inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool,
   const int hw = (dv8 <= 16 && H > kTcWarps) ? 2 : 1;
   const int gs = has_talk ? G : std::min(G, (kTcWarps * hw + H / G - 1) / (H / G) + 1);
   const bool alias = same_pool && dk == dvp;
-  size_t bytes = static_cast<size_t>(gs) * kTcKeys * (dk + 8) * 2;
-  if (!alias) bytes += static_cast<size_t>(gs) * kTcKeys * (dvp + 8) * 2;
-  if (has_talk) bytes += sizeof(float) * (static_cast<size_t>(H) * kTcRows * kTcRawStride + static_cast<size_t>(kTcWarps) * hw * H);
-  if (unrotate) bytes = std::max(bytes, sizeof(float) * kTcWarps * kTcRows * static_cast<size_t>(dvp));
-  if (bytes > 227 * 1024) return false;
-  if (plan) *plan = TcPlan{dv8, hw, bytes};
+  size_t stage = static_cast<size_t>(gs) * kTcKeys * (dk + 8) * 2;
+  if (!alias) stage += static_cast<size_t>(gs) * kTcKeys * (dvp + 8) * 2;
+  size_t rest = 0;
+  if (has_talk) rest = sizeof(float) * (static_cast<size_t>(H) * kTcRows * kTcRawStride + static_cast<size_t>(kTcWarps) * hw * H);
+  const size_t slab = unrotate ? sizeof(float) * kTcWarps * kTcRows * static_cast<size_t>(dvp) : 0;
+  const size_t cap = 227 * 1024;
+  int stages = 2;
+  if (std::max(2 * stage + rest, slab) > cap) stages = 1;
+  const size_t bytes = std::max(stages * stage + rest, slab);
+  if (bytes > cap) return false;
+  if (plan) *plan = TcPlan{dv8, hw, stages, bytes};
   return true;
 }
 
@@ -840,11 +942,11 @@ causal_conv_silu_kernel(T* __restrict__ out, int64_t out_stride, const T* __rest
 // ---- gated delta rule --------------------------------------------------------------------------------------------
 // One CTA per (sequence, head, 32 value columns): a value column's part of the state never meets another column's, so
 // columns are independent.  Four adjacent lanes share a column; lane r keeps the state rows i = r, r + 4, ... of that
-// column in registers for the whole portion.  Four tokens are staged at a time: their activated q and k (unit length
-// per head, q also scaled), the decays g = exp(-exp(A_log) softplus(a + dt_bias)), the write strength sigmoid(b) and
-// the CTA's value columns.  Per token: S <- g S and d = S^T k in one pass, u = beta (v - d), then S <- S + k u and
+// column in registers for the whole portion.  Eight tokens (fewer for the widest keys) are staged at a time, double buffered (the raw loads of
+// the next eight are issued before the current eight are computed): their activated q and k (unit length per head, q
+// also scaled), the decays g = exp(-exp(A_log) softplus(a + dt_bias)), the write strength sigmoid(b) and the CTA's
+// value columns.  Per token: S <- g S and d = S^T k in one pass, u = beta (v - d), then S <- S + k u and
 // o = S^T q in a second pass; the four lanes' partial sums meet in two shuffles.
-constexpr int kDeltaChunk = 4;
 constexpr int kDeltaNT = 128;
 constexpr int kDeltaCols = kDeltaNT / 4;
 
@@ -858,12 +960,16 @@ struct DeltaArgs {
   int H, G, dk, dv; float unit_eps, q_scale;
 };
 
+__host__ __device__ constexpr int delta_chunk(int dk_padded) { return dk_padded >= 256 ? 2 : (dk_padded >= 128 ? 4 : 8); }
+
 template <typename T, int DK>
 __global__ void __launch_bounds__(kDeltaNT)
 delta_scan_kernel(const DeltaArgs A) {
   extern __shared__ __align__(16) float smem[];
   constexpr int RW4 = DK / 4;
+  constexpr int kDeltaChunk = delta_chunk(DK);
   constexpr int row_len = 3 * DK + kDeltaCols + 4;      // q | k | g (each grouped by r) | v[32] | beta, pad
+  constexpr int kPer = (kDeltaChunk * row_len + kDeltaNT - 1) / kDeltaNT;   // staged elements per thread and chunk
   const SeqSpan sq = A.seqs[blockIdx.x];
   const int h = blockIdx.y, H = A.H, dk = A.dk, dv = A.dv;
   const int gq = h / (H / A.G);                          // the q / k head this value head reads
@@ -886,34 +992,56 @@ delta_scan_kernel(const DeltaArgs A) {
   const T* dtb = static_cast<const T*>(A.dt_bias);
   const float a_rate = expf(Cvt<T>::to_f32(static_cast<const T*>(A.a_log)[h]));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int t0 = 0; t0 < sq.count; t0 += kDeltaChunk) {
-    const int n_here = min(kDeltaChunk, sq.count - t0);
-    __syncthreads();          // the previous chunk has been consumed
-    for (int e = threadIdx.x; e < n_here * row_len; e += kDeltaNT) {
+  float* buf0 = smem;
+  float* buf1 = smem + kDeltaChunk * row_len;
+  T rawv[kPer];
+  // staged element e of a chunk: token e / row_len, slot e % row_len; slot r * RW4 + kk of a section holds row 4 kk + r.
+  // `fetch` only issues the loads (nothing waits for them until `commit`), so they fly while a chunk is computed.
+  auto fetch = [&](int t0) {
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      const int e = threadIdx.x + u * kDeltaNT;
       const int tt = e / row_len, sl = e - tt * row_len;
-      const int64_t tok = sq.tok0 + t0 + tt;
-      float val = 0.f;
-      if (sl < 3 * DK) {
-        const int which = sl / DK, s2 = sl - which * DK;
-        const int i = 4 * (s2 % RW4) + s2 / RW4;         // slot r * RW4 + kk holds row 4 kk + r
-        if (i < dk) {
-          if (which == 0) val = Cvt<T>::to_f32(qp[tok * A.in_stride + gq * dk + i]);
-          else if (which == 1) val = Cvt<T>::to_f32(kp[tok * A.in_stride + gq * dk + i]);
-          else
-            val = expf(-a_rate * softplus_(Cvt<T>::to_f32(ap[tok * A.a_stride + h * dk + i]) +
-                                           Cvt<T>::to_f32(dtb[h * dk + i])));
+      rawv[u] = Cvt<T>::from_f32(0.f);
+      if (tt < kDeltaChunk && t0 + tt < sq.count) {
+        const int64_t tok = sq.tok0 + t0 + tt;
+        if (sl < 3 * DK) {
+          const int which = sl / DK, s2 = sl - which * DK;
+          const int i = 4 * (s2 % RW4) + s2 / RW4;
+          if (i < dk) {
+            if (which == 0) rawv[u] = qp[tok * A.in_stride + gq * dk + i];
+            else if (which == 1) rawv[u] = kp[tok * A.in_stride + gq * dk + i];
+            else rawv[u] = ap[tok * A.a_stride + h * dk + i];
+          }
+        } else if (sl < 3 * DK + kDeltaCols) {
+          if (sl - 3 * DK < ncol) rawv[u] = vp[tok * A.in_stride + h * dv + col0 + sl - 3 * DK];
+        } else if (sl == 3 * DK + kDeltaCols) {
+          rawv[u] = bp[tok * A.beta_stride + h];
         }
-      } else if (sl < 3 * DK + kDeltaCols) {
-        const int c = sl - 3 * DK;
-        if (c < ncol) val = Cvt<T>::to_f32(vp[tok * A.in_stride + h * dv + col0 + c]);
-      } else if (sl == 3 * DK + kDeltaCols) {
-        val = sigmoid_(Cvt<T>::to_f32(bp[tok * A.beta_stride + h]));
       }
-      smem[e] = val;
     }
-    __syncthreads();
-    if (warp < n_here) {      // warp w brings token w's q and k to unit length
-      float* row = smem + warp * row_len;
+  };
+  auto commit = [&](float* dst, int n_valid) {
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      const int e = threadIdx.x + u * kDeltaNT;
+      const int tt = e / row_len, sl = e - tt * row_len;
+      if (tt < n_valid) {
+        float val = Cvt<T>::to_f32(rawv[u]);
+        if (sl >= 2 * DK && sl < 3 * DK) {
+          const int s2 = sl - 2 * DK;
+          const int i = 4 * (s2 % RW4) + s2 / RW4;
+          val = i < dk ? expf(-a_rate * softplus_(val + Cvt<T>::to_f32(dtb[h * dk + i]))) : 0.f;
+        } else if (sl == 3 * DK + kDeltaCols) {
+          val = sigmoid_(val);
+        }
+        dst[e] = val;
+      }
+    }
+  };
+  auto unit = [&](float* dst, int n_valid) {   // warp w brings tokens w, w + 4, ... to unit length per head
+    for (int tt = warp; tt < n_valid; tt += kDeltaNT / 32) {
+      float* row = dst + tt * row_len;
       float sq2 = 0.f, sk2 = 0.f;
       for (int i = lane; i < DK; i += 32) {
         sq2 = fmaf(row[i], row[i], sq2);
@@ -926,20 +1054,37 @@ delta_scan_kernel(const DeltaArgs A) {
         row[DK + i] *= ik;
       }
     }
-    __syncthreads();
+  };
+  fetch(0);
+  commit(buf0, min(kDeltaChunk, sq.count));
+  __syncthreads();
+  unit(buf0, min(kDeltaChunk, sq.count));
+  __syncthreads();
+  for (int t0 = 0; t0 < sq.count; t0 += kDeltaChunk) {
+    const float* cur = ((t0 / kDeltaChunk) & 1) ? buf1 : buf0;
+    float* nxt = ((t0 / kDeltaChunk) & 1) ? buf0 : buf1;
+    const int n_here = min(kDeltaChunk, sq.count - t0);
+    const int n_next = min(kDeltaChunk, sq.count - t0 - kDeltaChunk);
+    if (n_next > 0) fetch(t0 + kDeltaChunk);
     for (int tt = 0; tt < n_here; ++tt) {
-      const float* row = smem + tt * row_len;
+      const float* row = cur + tt * row_len;
       const float* qr = row + r * RW4;
       const float* kr = row + DK + r * RW4;
       const float* gr = row + 2 * DK + r * RW4;
       const float vc = row[3 * DK + cl], beta = row[3 * DK + kDeltaCols];
       float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-      for (int kk = 0; kk < RW4; kk += 2) {
-        S[kk] *= gr[kk];
-        d0 = fmaf(S[kk], kr[kk], d0);
-        S[kk + 1] *= gr[kk + 1];
-        d1 = fmaf(S[kk + 1], kr[kk + 1], d1);
+      for (int kk = 0; kk < RW4; kk += 4) {
+        const float4 g4 = *reinterpret_cast<const float4*>(gr + kk);
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + kk);
+        S[kk] *= g4.x;
+        d0 = fmaf(S[kk], k4.x, d0);
+        S[kk + 1] *= g4.y;
+        d1 = fmaf(S[kk + 1], k4.y, d1);
+        S[kk + 2] *= g4.z;
+        d0 = fmaf(S[kk + 2], k4.z, d0);
+        S[kk + 3] *= g4.w;
+        d1 = fmaf(S[kk + 3], k4.w, d1);
       }
       float d = d0 + d1;
       d += __shfl_xor_sync(0xffffffffu, d, 1);
@@ -947,17 +1092,29 @@ delta_scan_kernel(const DeltaArgs A) {
       const float u = beta * (vc - d);
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-      for (int kk = 0; kk < RW4; kk += 2) {
-        S[kk] = fmaf(kr[kk], u, S[kk]);
-        o0 = fmaf(S[kk], qr[kk], o0);
-        S[kk + 1] = fmaf(kr[kk + 1], u, S[kk + 1]);
-        o1 = fmaf(S[kk + 1], qr[kk + 1], o1);
+      for (int kk = 0; kk < RW4; kk += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + kk);
+        const float4 q4 = *reinterpret_cast<const float4*>(qr + kk);
+        S[kk] = fmaf(k4.x, u, S[kk]);
+        o0 = fmaf(S[kk], q4.x, o0);
+        S[kk + 1] = fmaf(k4.y, u, S[kk + 1]);
+        o1 = fmaf(S[kk + 1], q4.y, o1);
+        S[kk + 2] = fmaf(k4.z, u, S[kk + 2]);
+        o0 = fmaf(S[kk + 2], q4.z, o0);
+        S[kk + 3] = fmaf(k4.w, u, S[kk + 3]);
+        o1 = fmaf(S[kk + 3], q4.w, o1);
       }
       float o = o0 + o1;
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       if (r == 0 && has_col) A.o_raw[(static_cast<int64_t>(sq.tok0 + t0 + tt) * H + h) * dv + col] = o;
     }
+    if (n_next > 0) {
+      commit(nxt, n_next);       // `nxt` was last read two chunks ago, before the barrier that ended that chunk
+      __syncthreads();
+      unit(nxt, n_next);
+    }
+    __syncthreads();
   }
 #pragma unroll
   for (int kk = 0; kk < RW4; ++kk) {
@@ -1122,16 +1279,33 @@ int b200_mixed_prompt_attn_supported(int H, int G, int dk, int dv, int has_talk,
   return tc_plan(H, G, dk, dv, has_talk != 0, same_pool != 0, unrotate != 0, dtype, nullptr) ? 1 : 0;
 }
 
+int b200_mixed_prompt_attn_splits(int n_tiles, int key_tiles, int H, int G, int dk, int dv, int has_talk, int same_pool,
+                                  int unrotate, int dtype) {
+  TcPlan plan;
+  if (n_tiles <= 0 || H <= 0 || G <= 0 || !tc_plan(H, G, dk, dv, has_talk != 0, same_pool != 0, unrotate != 0, dtype, &plan))
+    return 1;
+  const int ctas = n_tiles * ((H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw));
+  if (ctas >= kNumSMs) return 1;
+  return std::max(1, std::min({8, (2 * kNumSMs + ctas - 1) / ctas, key_tiles / 4}));
+}
+
+size_t b200_mixed_prompt_attn_workspace(int n_splits, int n_tok, int H, int dv) {
+  if (n_splits <= 1 || n_tok <= 0 || H <= 0 || dv <= 0) return 0;
+  const int dvp = (dv <= 64 ? 8 : (dv <= 128 ? 16 : 32)) * 8;
+  return sizeof(float) * static_cast<size_t>(n_splits) * n_tok * H * (dvp + 2);
+}
+
 int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q, int64_t q_tok_stride,
                            int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
                            const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tiles,
-                           int n_tiles, const int32_t* tok_pos, const float* talk, const float* sink, float scale,
-                           int window, int keep_first, const float* value_rot, int interleaved, int H, int G, int dk,
-                           int dv, int block_size, int dtype, void* stream) {
-  if (n_tiles < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0)
+                           int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk, const float* sink,
+                           float scale, int window, int keep_first, const float* value_rot, int interleaved, int H, int G,
+                           int dk, int dv, int block_size, int n_splits, float* workspace, int dtype, void* stream) {
+  if (n_tiles < 0 || n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0 || n_splits < 1 ||
+      n_splits > 64)
     return fail(B200_EINVAL, "b200_mixed_prompt_attn: bad sizes");
   if (n_tiles == 0) return 0;
-  if (!out || !q || !k_pool || !v_pool || !block_tables || !tiles || !tok_pos)
+  if (!out || !q || !k_pool || !v_pool || !block_tables || !tiles || !tok_pos || (n_splits > 1 && !workspace))
     return fail(B200_EINVAL, "b200_mixed_prompt_attn: null pointer");
   if ((q_tok_stride | q_head_stride | out_tok_stride | out_head_stride) & 1)
     return fail(B200_ESHAPE, "b200_mixed_prompt_attn: odd strides");
@@ -1141,23 +1315,31 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, nullptr, tok_pos, talk, sink, scale, window, keep_first, value_rot != nullptr,
              interleaved, 0.0, H, G, dk, dv, block_size};
-  const dim3 grid(n_tiles, (H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw));
+  const dim3 grid(n_tiles, (H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw), n_splits);
   return hybrid_by_dtype(dtype, "b200_mixed_prompt_attn", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
     if constexpr (std::is_same_v<T, float>) {
       return fail(B200_ESHAPE, "b200_mixed_prompt_attn: 16-bit storage types only");
     } else {
+      auto s = static_cast<cudaStream_t>(stream);
       auto launch = [&](auto kern) {
         if (plan.smem > 48 * 1024)
           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem));
-        kern<<<grid, kTcWarps * 32, plan.smem, static_cast<cudaStream_t>(stream)>>>(A, tiles, value_rot);
+        kern<<<grid, kTcWarps * 32, plan.smem, s>>>(A, tiles, value_rot, workspace, n_tok, plan.stages);
       };
       if (plan.dv8 == 8 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 8, 1>);
       else if (plan.dv8 == 8) launch(mixed_prompt_attn_kernel<T, 8, 2>);
       else if (plan.dv8 == 16 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 16, 1>);
       else if (plan.dv8 == 16) launch(mixed_prompt_attn_kernel<T, 16, 2>);
       else launch(mixed_prompt_attn_kernel<T, 32, 1>);
-      return check_launch("b200_mixed_prompt_attn");
+      int rc = check_launch("b200_mixed_prompt_attn");
+      if (rc != 0 || n_splits == 1) return rc;
+      // every packed row belongs to exactly one tile, so the merge runs over all rows
+      const size_t smem_c = sizeof(float) * static_cast<size_t>(H) * dv;
+      auto comb = attn_split_combine_kernel<T>;
+      if (smem_c > 48 * 1024) cudaFuncSetAttribute(comb, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_c));
+      comb<<<n_tok, 256, smem_c, s>>>(A, workspace, n_splits, n_tok, plan.dv8 * 8, value_rot);
+      return check_launch("b200_mixed_prompt_attn (merge)");
     }
   });
 }
@@ -1188,17 +1370,21 @@ int b200_delta_scan(float* o_raw, const void* q, const void* k, const void* v, i
   if (!o_raw || !q || !k || !v || !beta_logit || !a_logit || !dt_bias || !a_log || !state || !seqs)
     return fail(B200_EINVAL, "b200_delta_scan: null pointer");
   const int dkt = dk <= 32 ? 32 : (dk <= 64 ? 64 : (dk <= 128 ? 128 : 256));
-  const size_t smem = sizeof(float) * kDeltaChunk * (3 * static_cast<size_t>(dkt) + kDeltaCols + 4);
+  const size_t smem = sizeof(float) * 2 * delta_chunk(dkt) * (3 * static_cast<size_t>(dkt) + kDeltaCols + 4);
   const dim3 grid(n_seqs, H, (dv + kDeltaCols - 1) / kDeltaCols);
   DeltaArgs A{o_raw, q, k, v, in_stride, beta_logit, beta_stride, a_logit, a_stride, dt_bias, a_log, state,
               reinterpret_cast<const SeqSpan*>(seqs), H, G, dk, dv, unit_eps, q_scale};
   return hybrid_by_dtype(dtype, "b200_delta_scan", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
     auto s = static_cast<cudaStream_t>(stream);
-    if (dkt == 32) delta_scan_kernel<T, 32><<<grid, kDeltaNT, smem, s>>>(A);
-    else if (dkt == 64) delta_scan_kernel<T, 64><<<grid, kDeltaNT, smem, s>>>(A);
-    else if (dkt == 128) delta_scan_kernel<T, 128><<<grid, kDeltaNT, smem, s>>>(A);
-    else delta_scan_kernel<T, 256><<<grid, kDeltaNT, smem, s>>>(A);
+    auto launch = [&](auto kern) {
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      kern<<<grid, kDeltaNT, smem, s>>>(A);
+    };
+    if (dkt == 32) launch(delta_scan_kernel<T, 32>);
+    else if (dkt == 64) launch(delta_scan_kernel<T, 64>);
+    else if (dkt == 128) launch(delta_scan_kernel<T, 128>);
+    else launch(delta_scan_kernel<T, 256>);
     return check_launch("b200_delta_scan");
   });
 }

@@ -437,10 +437,12 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
                            block_tables: torch.Tensor, tiles: torch.Tensor, tok_pos: torch.Tensor, scale: float,
                            talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
                            keep_first: int = 0, value_rot: Optional[torch.Tensor] = None, interleaved: bool = False,
-                           gate: Optional[torch.Tensor] = None) -> None:
+                           gate: Optional[torch.Tensor] = None, max_context: int = 0) -> None:
     """``mixed_paged_attention`` on the tensor cores for prompt portions and decoded tokens alike (16-bit dtypes, see
     ``mixed_prompt_attention_supported``).  ``tiles`` int32 ``[n_tiles, 3]``: up to ``PROMPT_TILE_TOKENS`` consecutive
-    tokens of one sequence each; ``value_rot``: the table ``rotary_kv_append`` returned for this step's tokens."""
+    tokens of one sequence each, together covering every row of ``q``; ``value_rot``: the table ``rotary_kv_append``
+    returned for this step's tokens; ``max_context``: the longest context of the step (a hint: steps of few tokens over
+    long contexts divide the keys over several CTAs and merge)."""
     _need_cuda(out, q, k_pool, v_pool, block_tables, tiles, tok_pos)
     nb, G, bs, dk = k_pool.shape
     dv = v_pool.shape[3]
@@ -459,12 +461,20 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
         raise ValueError("value_rot must be contiguous fp32 [n, dv // 2, 2]")
     if gate is not None and (tuple(gate.shape) != (n, H) or gate.dtype != q.dtype):
         raise ValueError("gate must be [n, H] in the activations' dtype")
-    rc = _lib_().b200_mixed_prompt_attn(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
-                                        _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
-                                        v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(),
-                                        tiles.shape[0], tok_pos.data_ptr(), _ptr(talk), _ptr(sink), float(scale), int(window),
-                                        int(keep_first), _ptr(value_rot), int(interleaved), H, G, dk, dv, bs,
-                                        DTYPE_ID[q.dtype], _stream())
+    lib = _lib_()
+    seen = min(max_context, window + keep_first + PROMPT_TILE_TOKENS) if window > 0 else max_context
+    splits = lib.b200_mixed_prompt_attn_splits(tiles.shape[0], (seen + 31) // 32, H, G, dk, dv, int(talk is not None),
+                                               int(k_pool.data_ptr() == v_pool.data_ptr()), int(value_rot is not None),
+                                               DTYPE_ID[q.dtype]) if max_context > 0 else 1
+    ws = None
+    if splits > 1:
+        ws = torch.empty(lib.b200_mixed_prompt_attn_workspace(splits, n, H, dv) // 4, dtype=torch.float32, device=q.device)
+    rc = lib.b200_mixed_prompt_attn(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
+                                    _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
+                                    v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(),
+                                    tiles.shape[0], tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink), float(scale), int(window),
+                                    int(keep_first), _ptr(value_rot), int(interleaved), H, G, dk, dv, bs, int(splits),
+                                    _ptr(ws), DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_prompt_attn")
 
 

@@ -193,6 +193,10 @@ class RaggedBatchState:
     pending_norm: Optional[torch.Tensor] = None
     _tiles: Optional[dict] = None
 
+    def max_context(self) -> int:
+        """Tokens of the longest sequence of the step, this step's included."""
+        return max(past + count for _first, count, _row, past in self.spans)
+
     def tiles_for(self, num_heads: int, num_kv_heads: int, below: int = 0):
         """``(tiles int32 [n, 3], tokens per tile at most)`` for an attention layer with this head layout: each
         sequence's tokens cut into runs that one CTA of ``biased_paged_attention`` serves, longest context first.

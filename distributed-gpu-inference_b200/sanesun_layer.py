@@ -169,7 +169,7 @@ class WindowedSinkAttention(nn.Module):
             mixer_ops.mixed_prompt_attention(attn, q.unflatten(1, (H, dk)), cache.k_pool, cache.v_pool, st.block_tables,
                                              tiles, st.tok_pos, self.scale, talk=self.talk, sink=self.sink,
                                              window=self.window, keep_first=self.keep_first, value_rot=table,
-                                             interleaved=self.interleaved)
+                                             interleaved=self.interleaved, max_context=st.max_context())
         else:                     # fp32, or head sizes off the tensor-core grid: the row kernel
             mixer_ops.mixed_paged_attention(attn, q.unflatten(1, (H, dk)), cache.k_pool, cache.v_pool, st.block_tables,
                                             st.tok_row, st.tok_pos, self.scale, talk=self.talk, sink=self.sink,
@@ -215,7 +215,8 @@ class LatentAttention(nn.Module):
         if self.tensor_cores:
             tiles, _ = st.prompt_tiles(1, mixer_ops.PROMPT_TILE_TOKENS)
             mixer_ops.mixed_prompt_attention(o_lat.transpose(0, 1), q_lat.transpose(0, 1), cache.k_pool, cache.k_pool,
-                                             st.block_tables, tiles, st.tok_pos, self.scale, gate=proj[:, c[2]:c[2] + H])
+                                             st.block_tables, tiles, st.tok_pos, self.scale, gate=proj[:, c[2]:c[2] + H],
+                                             max_context=st.max_context())
         else:
             mixer_ops.mixed_paged_attention(o_lat.transpose(0, 1), q_lat.transpose(0, 1), cache.k_pool, cache.k_pool,
                                             st.block_tables, st.tok_row, st.tok_pos, self.scale,

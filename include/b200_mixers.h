@@ -163,12 +163,20 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
  * one sequence.  Outputs are turned back when value_rot (the table b200_rotary_kv_append wrote for these tokens) is
  * given.  Scores, mask and softmax are fp32; the weights are rounded to T only as the operand of the P.V product. */
 int b200_mixed_prompt_attn_supported(int H, int G, int dk, int dv, int has_talk, int same_pool, int unrotate, int dtype);
+/* Steps of few tokens leave most SMs idle: with n_splits > 1 the key tiles of every query tile are divided over
+ * n_splits CTAs, which leave (max, sum, unnormalised output) in `workspace` (fp32, b200_mixed_prompt_attn_workspace
+ * bytes), and a second launch merges them.  b200_mixed_prompt_attn_splits proposes n_splits for a step of n_tiles
+ * query tiles whose longest walk is key_tiles tiles of 32 keys.  n_tok: packed rows of the step (every row lies in
+ * exactly one tile). */
+int b200_mixed_prompt_attn_splits(int n_tiles, int key_tiles, int H, int G, int dk, int dv, int has_talk, int same_pool,
+                                  int unrotate, int dtype);
+size_t b200_mixed_prompt_attn_workspace(int n_splits, int n_tok, int H, int dv);
 int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q, int64_t q_tok_stride,
                            int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
                            const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tiles,
-                           int n_tiles, const int32_t* tok_pos, const float* talk, const float* sink, float scale,
-                           int window, int keep_first, const float* value_rot, int interleaved, int H, int G, int dk,
-                           int dv, int block_size, int dtype, void* stream);
+                           int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk, const float* sink,
+                           float scale, int window, int keep_first, const float* value_rot, int interleaved, int H, int G,
+                           int dk, int dv, int block_size, int n_splits, float* workspace, int dtype, void* stream);
 
 /* out[t, c] = silu(sum_i w[c][i] * x[t - (taps - 1 - i), c]) per sequence (SeqSpan rows); inputs before the portion
  * come from tail [slots, taps - 1, C] (fp32, oldest first), which then receives the portion's last taps - 1 inputs. */

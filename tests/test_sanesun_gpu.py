@@ -276,6 +276,14 @@ def test_tensor_core_attention_matches_the_statement(dt, H, G, dk, dv, mixing):
     assert torch.isfinite(got).all()
     err = (got[rows] - ref[rows]).abs().max().item()
     assert err <= 2e-2 * max(1.0, ref[rows].abs().max().item()), err
+    # the same step with its keys divided over several CTAs and merged (what steps of few tokens do); the hint is made
+    # large so that some CTAs get no key tile at all
+    out3 = torch.full((n, H, dv), float("nan"), dtype=dt, device=DEV)
+    M.mixed_prompt_attention(out3, q.to(DEV), kp, vp, table, torch.tensor(tiles, dtype=torch.int32, device=DEV),
+                             pos.to(torch.int32).to(DEV), 0.3, talk=None if talk is None else talk.to(DEV),
+                             sink=None if sink is None else sink.to(DEV), window=size, keep_first=keep, value_rot=tab,
+                             gate=None if gate is None else gate.to(DEV), max_context=1 << 14)
+    assert (out3.float() - out.float()).abs().max().item() <= 1e-2 * max(1.0, ref[rows].abs().max().item())
     # the row kernel is the fp32 / odd-size fallback of the same contract: both agree on every row
     out2 = torch.empty_like(out)
     M.mixed_paged_attention(out2, q.to(DEV), kp, vp, table, torch.zeros(n, dtype=torch.int32, device=DEV),
@@ -302,6 +310,15 @@ def test_tensor_core_latent_attention_reads_one_pool_for_keys_and_values():
     ref = R.windowed_attention(q.to(F64), c.to(F64), c.to(F64), 0.09, rows=rows)
     got = out.transpose(0, 1).cpu().to(F64)
     assert (got[rows] - ref[rows]).abs().max().item() <= 2e-2 * ref[rows].abs().max().item()
+    # three decoded tokens of long contexts: few CTAs, so the keys are split and merged
+    last = torch.tensor([n - 3, n - 2, n - 1])
+    out = torch.empty((H, 3, r), dtype=torch.bfloat16, device=DEV)
+    M.mixed_prompt_attention(out.transpose(0, 1), q[last].to(DEV), kp, kp, table.expand(3, -1).contiguous(),
+                             torch.tensor([(0, 1, 0), (1, 1, 1), (2, 1, 2)], dtype=torch.int32, device=DEV),
+                             last.to(torch.int32).to(DEV), 0.09, max_context=n)
+    assert M._lib_().b200_mixed_prompt_attn_splits(3, (n + 31) // 32, H, 1, r, r, 0, 1, 0, 2) > 1
+    ref = R.windowed_attention(q.to(F64), c.to(F64), c.to(F64), 0.09, rows=last.tolist())
+    assert (out.transpose(0, 1).cpu().to(F64) - ref[last]).abs().max().item() <= 2e-2 * ref[last].abs().max().item()
     w = torch.softmax((c[: i + 1, 0].to(F64) @ q[i, 2].to(F64)) * 0.09, 0)
     assert w[far] > 0.9
 
