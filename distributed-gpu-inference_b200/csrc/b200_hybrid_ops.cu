@@ -106,17 +106,25 @@ residual_add2_norm_kernel(float* __restrict__ x, const T* __restrict__ a, int64_
 // ---- xIELU -------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
-xielu_kernel(T* __restrict__ out, const T* __restrict__ z, int64_t z_stride, const T* __restrict__ pq, int ff,
-             int64_t total) {
+xielu_kernel(T* __restrict__ out, const T* __restrict__ z, int64_t z_stride, const T* __restrict__ pq, int ff, bool vec) {
+  // one row per blockIdx.y; 16-byte accesses when the rows allow it
   const float ap = softplus_(Cvt<T>::to_f32(pq[0]));
   const float an = 0.5f + softplus_(Cvt<T>::to_f32(pq[1]));
-  for (int64_t e = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
-       e += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-    const int64_t r = e / ff;
-    const int c = static_cast<int>(e - r * ff);
-    const float v = Cvt<T>::to_f32(z[r * z_stride + c]);
-    const float y = v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v);
-    out[e] = Cvt<T>::from_f32(y);
+  const T* zr = z + static_cast<int64_t>(blockIdx.y) * z_stride;
+  T* orow = out + static_cast<int64_t>(blockIdx.y) * ff;
+  auto act = [&](float v) { return v > 0.f ? fmaf(ap * v, v, 0.5f * v) : fmaf(an, expm1f(v) - v, 0.5f * v); };
+  if (vec) {
+    constexpr int E = 16 / sizeof(T);
+    for (int c = (blockIdx.x * blockDim.x + threadIdx.x) * E; c < ff; c += gridDim.x * blockDim.x * E) {
+      int4 raw = *reinterpret_cast<const int4*>(zr + c);
+      T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+      for (int u = 0; u < E; ++u) e[u] = Cvt<T>::from_f32(act(Cvt<T>::to_f32(e[u])));
+      *reinterpret_cast<int4*>(orow + c) = raw;
+    }
+  } else {
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < ff; c += gridDim.x * blockDim.x)
+      orow[c] = Cvt<T>::from_f32(act(Cvt<T>::to_f32(zr[c])));
   }
 }
 
@@ -488,7 +496,7 @@ constexpr int kTcRows = 16;
 constexpr int kTcRawStride = 40;
 
 template <typename T, int DV8, int HW>
-__global__ void __launch_bounds__(kTcWarps * 32)
+__global__ void __launch_bounds__(kTcWarps * 32, (HW == 1 && DV8 <= 16) ? 2 : 1)
 mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, const float* __restrict__ rot_tab,
                          float* __restrict__ ws, int n_tok, int stages) {
   extern __shared__ __align__(16) unsigned char tc_smem[];
@@ -1192,12 +1200,14 @@ int b200_xielu(void* out, const void* z, int64_t z_stride, const void* pq, int r
   if (rows < 0 || ff <= 0) return fail(B200_EINVAL, "b200_xielu: bad sizes");
   if (rows == 0) return 0;
   if (!out || !z || !pq) return fail(B200_EINVAL, "b200_xielu: null pointer");
-  const int64_t total = static_cast<int64_t>(rows) * ff;
-  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 16));
+  const int es = dtype_size(dtype);
+  const bool vec = es > 0 && (ff * es) % 16 == 0 && (z_stride * es) % 16 == 0 && aligned16(z) && aligned16(out);
+  const int per = vec ? 256 * (16 / es) : 256;
+  const dim3 grid(std::min((ff + per - 1) / per, 64), rows);
   return hybrid_by_dtype(dtype, "b200_xielu", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
     xielu_kernel<T><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<T*>(out), static_cast<const T*>(z),
-                                                                         z_stride, static_cast<const T*>(pq), ff, total);
+                                                                         z_stride, static_cast<const T*>(pq), ff, vec);
     return check_launch("b200_xielu");
   });
 }
@@ -1325,6 +1335,7 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
       auto launch = [&](auto kern) {
         if (plan.smem > 48 * 1024)
           cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(plan.smem));
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         kern<<<grid, kTcWarps * 32, plan.smem, s>>>(A, tiles, value_rot, workspace, n_tok, plan.stages);
       };
       if (plan.dv8 == 8 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 8, 1>);
