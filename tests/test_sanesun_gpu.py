@@ -284,7 +284,7 @@ def test_tensor_core_attention_matches_the_statement(dt, H, G, dk, dv, mixing):
                              sink=None if sink is None else sink.to(DEV), window=size, keep_first=keep, value_rot=tab,
                              gate=None if gate is None else gate.to(DEV), max_context=1 << 14)
     assert (out3.float() - out.float()).abs().max().item() <= 1e-2 * max(1.0, ref[rows].abs().max().item())
-    # the row kernel is the fp32 / odd-size fallback of the same contract: both agree on every row
+    # the row kernel is the fp32 / odd-size fallback for the same operation: both agree on every row
     out2 = torch.empty_like(out)
     M.mixed_paged_attention(out2, q.to(DEV), kp, vp, table, torch.zeros(n, dtype=torch.int32, device=DEV),
                             pos.to(torch.int32).to(DEV), 0.3, talk=None if talk is None else talk.to(DEV),
